@@ -9,6 +9,8 @@ Host-side bookkeeping only (integers, no tensors); the tensors live in
 * A group with a window gives a page back as soon as no later query can read it: after ``c``
   tokens are computed, the next query sits at position ``c`` and reads keys ``>= c-window+1``, so
   page ``i`` is released once ``(i+1)*page_tokens <= c-window+1``. Its table entry becomes -1.
+  A group whose queries also read the request's first ``keep_first`` tokens whatever the window
+  never releases the pages that hold any of those.
 * Each live request also holds one *state slot*, an index below ``max_requests``, which selects
   its row in every fixed-size per-request state tensor. The Llama architecture keeps nothing
   there; the slot exists so that a mixer with a recurrent state finds a place for it.
@@ -38,6 +40,12 @@ class KVGroupSpec:
     page_tokens: int
     dtype: object = None  # of the pages; None: the model's compute dtype
     planes: int = 2  # 2: a key row and a value row per token; 1: one row that is both
+    keep_first: int = 0  # with a window: the first tokens of a request that stay readable for good
+
+    @property
+    def kept_pages(self) -> int:
+        """Pages at the start of a request's table that a window never releases."""
+        return -(-self.keep_first // self.page_tokens) if self.window > 0 else 0
 
     def bytes_per_token(self, dtype_bytes: int) -> int:
         """``dtype_bytes``: element size of the compute dtype (used unless the group names its own)."""
@@ -54,7 +62,8 @@ class KVGroupSpec:
         if self.window <= 0:
             n = max_len
         else:
-            n = min(max_len, self.window - 1 + max_portion + self.page_tokens)
+            n = min(max_len, self.window - 1 + max_portion + self.page_tokens
+                    + self.kept_pages * self.page_tokens)
         return -(-n // self.page_tokens) * self.page_tokens
 
 
@@ -183,7 +192,7 @@ class CacheManager:
                 continue
             assert h.computed <= len(h.tables[g]) * spec.page_tokens, "committed past the table"
             first_needed = h.computed - spec.window + 1
-            i = 0
+            i = spec.kept_pages
             table = h.tables[g]
             while (i + 1) * spec.page_tokens <= first_needed and i < len(table):
                 if table[i] != RELEASED:

@@ -21,7 +21,7 @@ from .manager import KVGroupSpec, StateGroupSpec
 
 
 def group_cache_layers(needs: dict[int, object], page_tokens: int):
-    """Sort cache layers into key/value groups (same heads, head size, window and page dtype) and
+    """Sort cache layers into key/value groups (same heads, head size, window, kept first tokens and page dtype) and
     state groups. A cache layer may need several things at once (a tuple: at most one set of
     pages, any number of states): a state group lists such a layer once per state it holds there."""
     kv: dict[tuple, list[int]] = {}
@@ -34,13 +34,14 @@ def group_cache_layers(needs: dict[int, object], page_tokens: int):
                 if paged > 1:
                     raise TypeError(f"cache layer {cid}: more than one set of pages")
                 kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype,
-                               2 if need.values else 1), []).append(cid)
+                               2 if need.values else 1, need.keep_first if need.window > 0 else 0), []).append(cid)
             elif isinstance(need, StateNeed):
                 st.setdefault((tuple(need.shape), need.dtype), []).append(cid)
             else:
                 raise TypeError(f"cache layer {cid}: unknown need {need!r}")
     kv_groups = [
-        KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt, planes) for (nk, d, w, dt, planes), ids in kv.items()
+        KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt, planes, keep)
+        for (nk, d, w, dt, planes, keep), ids in kv.items()
     ]
     state_groups = [StateGroupSpec(tuple(ids), shape, dt) for (shape, dt), ids in st.items()]
     return kv_groups, state_groups

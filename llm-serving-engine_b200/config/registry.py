@@ -96,6 +96,18 @@ def _register_builtin() -> None:
             checkpoint_layout=pazivik_checkpoint_layout,
         )
     )
+    from ..models.rirovik import rirovik_checkpoint_layout, rirovik_plan
+    from .rirovik import RirovikConfig
+
+    register_architecture(
+        Architecture(
+            name="Rirovik",
+            model_type="rirovik",
+            config_cls=RirovikConfig,
+            plan=rirovik_plan,
+            checkpoint_layout=rirovik_checkpoint_layout,
+        )
+    )
 
 
 _register_builtin()

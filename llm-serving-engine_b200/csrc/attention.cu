@@ -88,6 +88,17 @@ __device__ __forceinline__ int first_key(const LseAttnArgs& a, int qpos) {
   if (a.chunk > 0) lo = max(lo, (qpos / a.chunk) * a.chunk);
   return lo;
 }
+// How many of the sequence's first keys a query block whose window starts at k_first reads beside
+// the window (keep_first): keys [0, kept) and [k_first, ...) are visible, [kept, k_first) are not.
+__device__ __forceinline__ int kept_keys(const LseAttnArgs& a, int k_first) {
+  return (a.keep_first > 0 && a.window > 0) ? min(a.keep_first, k_first) : 0;
+}
+// The tile after k0 in a walk over tiles of KT keys that skips the tiles wholly between the kept
+// keys and the window's first tile.
+__device__ __forceinline__ int next_tile(int k0, int KT, int kept_tiles_end, int window_tile) {
+  const int n = k0 + KT;
+  return (n >= kept_tiles_end && n < window_tile) ? window_tile : n;
+}
 __device__ __forceinline__ float head_factor(const LseAttnArgs& a, int head) {
   return a.head_scale ? a.scale * a.head_scale[head] : a.scale;
 }
@@ -128,14 +139,16 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
+  const int kept = kept_keys(a, k_first);
+  const int kept_tiles_end = (kept + KT - 1) / KT * KT, window_tile = (k_first / KT) * KT;
 
-  for (int k0 = (k_first / KT) * KT; k0 < k_end; k0 += KT) {
+  for (int k0 = kept > 0 ? 0 : window_tile; k0 < k_end; k0 = next_tile(k0, KT, kept_tiles_end, window_tile)) {
     __syncthreads();
     for (int idx = threadIdx.x; idx < KT * NCHUNK; idx += blockDim.x) {
       const int jj = idx / NCHUNK, c = idx - jj * NCHUNK;
       const int j = k0 + jj;
       Vec16<T> kv, vv;
-      if (j >= k_first && j < k_end) {
+      if ((j >= k_first || j < kept) && j < k_end) {
         int pi, off;
         page_of(j, a.page_tokens, page_shift, pi, off);
         const size_t base =
@@ -163,7 +176,7 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
       d += __shfl_xor_sync(0xffffffffu, d, 1);
       d += __shfl_xor_sync(0xffffffffu, d, 2);
       const int j = k0 + jj;
-      const bool ok = row_valid && j <= qpos && j >= q_first;
+      const bool ok = row_valid && j <= qpos && (j >= q_first || j < a.keep_first);
       s[jj] = ok ? d - slope * (float)(qpos - j) : -INFINITY;
       tile_max = fmaxf(tile_max, s[jj]);
     }
@@ -268,9 +281,11 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
   // With score options the scores are finished (factor, distance penalty) when they are masked,
   // and only the change to base 2 is left to the exponent's multiply-add.
-  const bool options = a.head_scale || a.slopes || a.chunk > 0 || a.sinks;
+  const bool options = a.head_scale || a.slopes || a.chunk > 0 || a.sinks || a.keep_first > 0;
   const float qk_factor = head_factor(a, head);
   const float slope = a.slopes ? a.slopes[head] : 0.f;
+  const int kept = kept_keys(a, k_first);
+  const int kept_tiles_end = (kept + KT - 1) / KT * KT;
   const float sl2 = (options ? 1.f : a.scale) * 1.4426950408889634f;  // scores in the base-2 domain
   const int qpos_r[2] = {si.pos0 + q0 + warp * 16 + g, si.pos0 + q0 + warp * 16 + g + 8};
   const int qfirst_r[2] = {first_key(a, qpos_r[0]), first_key(a, qpos_r[1])};
@@ -283,7 +298,7 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
     for (int idx = threadIdx.x; idx < KT * NCHUNK; idx += blockDim.x) {
       const int jj = idx / NCHUNK, c = idx - jj * NCHUNK;
       const int j = k0 + jj;
-      const bool ok = j >= k_first && j < k_end;
+      const bool ok = (j >= k_first || j < kept) && j < k_end;
       size_t base = 0;
       if (ok) {
         int pi, off;
@@ -295,12 +310,14 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
     }
     asm volatile("cp.async.commit_group;\n" ::);
   };
-  const int k_start = (k_first / KT) * KT;
+  const int window_tile = (k_first / KT) * KT;
+  const int k_start = kept > 0 ? 0 : window_tile;
   if (k_start < k_end) load_tile(0, k_start);
   int buf = 0;
-  for (int k0 = k_start; k0 < k_end; k0 += KT, buf ^= 1) {
-    if (k0 + KT < k_end) {
-      load_tile(buf ^ 1, k0 + KT);  // that buffer was released by the barrier that ended the last pass
+  for (int k0 = k_start; k0 < k_end; k0 = next_tile(k0, KT, kept_tiles_end, window_tile), buf ^= 1) {
+    const int k_next = next_tile(k0, KT, kept_tiles_end, window_tile);
+    if (k_next < k_end) {
+      load_tile(buf ^ 1, k_next);  // that buffer was released by the barrier that ended the last pass
       asm volatile("cp.async.wait_group 1;\n" ::);
     } else {
       asm volatile("cp.async.wait_group 0;\n" ::);
@@ -341,7 +358,7 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
         for (int e = 0; e < 4; ++e) {
           const int rr = e >> 1;
           const int j = k0 + nb * 8 + t4 * 2 + (e & 1);
-          const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= qfirst_r[rr];
+          const bool ok = valid_r[rr] && j <= qpos_r[rr] && (j >= qfirst_r[rr] || j < a.keep_first);
           const float sc = options ? s[nb][e] * qk_factor - slope * (float)(qpos_r[rr] - j) : s[nb][e];
           s[nb][e] = ok ? sc : -INFINITY;
           tmax[rr] = fmaxf(tmax[rr], s[nb][e]);
@@ -506,11 +523,16 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   const int seq = a.decode_seqs[b];
   const int tok = a.cu_q[seq];
   const int ctx = a.ctx_lens[seq];
+  // The keys this token reads, counted through: the kept first keys [0, kept), then the window
+  // [k_first, ctx). lo, hi and the loop's j are such counts; key_of() gives the key's position.
   const int k_first = first_key(a, ctx - 1);
-  const int span = ctx - k_first;
+  const int kept = kept_keys(a, k_first);
+  const int skipped = k_first - kept;
+  const int span = ctx - skipped;
   const int per = (span + a.num_splits - 1) / a.num_splits;
-  const int lo = k_first + split * per;
-  const int hi = min(ctx, lo + per);
+  const int lo = split * per;
+  const int hi = min(span, lo + per);
+  auto key_of = [&](int j) { return j < kept ? j : j + skipped; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int li = lane % LPK, slot = lane / LPK;
@@ -555,7 +577,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
       // a key past the end re-reads the last valid one (its result is dropped): no branch, so
       // every load of the U passes is issued before the first use
       int pi, off;
-      page_of(min(j, hi - 1), a.page_tokens, page_shift, pi, off);
+      page_of(key_of(min(j, hi - 1)), a.page_tokens, page_shift, pi, off);
       const size_t base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
 #pragma unroll
       for (int c = 0; c < CPL; ++c) {
@@ -585,7 +607,7 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
             d[u] = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[u][c].v[e]), d[u]);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
-        d[u] -= slope[gq] * (float)(ctx - 1 - (j0 + u * DEC_WARPS * KPI + slot));  // the distance penalty
+        d[u] -= slope[gq] * (float)(ctx - 1 - key_of(j0 + u * DEC_WARPS * KPI + slot));  // the distance penalty
         if (ok[u]) m_new = fmaxf(m_new, d[u]);  // ok is uniform over the LPK lanes of a key
       }
       const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;  // no key yet: everything stays 0
@@ -1616,7 +1638,8 @@ static int shift_of(int n) {
 static bool args_ok(const LseAttnArgs* a) {
   return a && (a->dtype == LSE_F32 || a->dtype == LSE_BF16) && a->num_heads > 0 &&
          a->num_kv_heads > 0 && a->num_heads % a->num_kv_heads == 0 && a->page_tokens > 0 &&
-         a->window >= 0 && a->chunk >= 0 && (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
+         a->window >= 0 && a->chunk >= 0 && a->keep_first >= 0 && !(a->keep_first > 0 && a->chunk > 0) &&
+         (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
          a->ctx_lens && a->cu_q;
 }
 
@@ -1624,7 +1647,8 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
-  const bool options = a->head_scale || a->slopes || a->chunk > 0 || a->sinks;  // served by the CUDA-core kernel only
+  const bool options = a->head_scale || a->slopes || a->chunk > 0 || a->sinks ||
+                       (a->keep_first > 0 && a->window > 0);  // served by the CUDA-core kernel only
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
   // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
   // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
@@ -1762,7 +1786,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
 #if LSE_HEAD_DIM == 64
   } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a) &&
-             !(a->head_scale || a->slopes || a->chunk > 0 || a->sinks)) {
+             !(a->head_scale || a->slopes || a->chunk > 0 || a->sinks || a->keep_first > 0)) {
     // 128-row tiles, like the mma.sync kernel
     return atc::launch_prefill(a, a->num_rows, a->num_pages * a->num_kv_heads * a->page_tokens,
                                a->error_flag, stream);

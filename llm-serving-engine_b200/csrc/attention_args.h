@@ -62,6 +62,10 @@ struct LseAttnArgs {
   //   sinks: the softmax's denominator also holds exp(sinks[h]), a term without key or value
   //   (not multiplied by scale); it counts once per query whatever the context's partitions are.
   const float* sinks;       // [num_heads] or null
+  //   keep_first > 0 (with a window, without chunks): beside the keys of its window a query also
+  //   reads the sequence's first keep_first keys, as far as they lie before it. The pages of those
+  //   keys must still be held.
+  int keep_first;
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)

@@ -312,7 +312,7 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
                      const Tensor& cu_q, const OptTensor& tiles, int64_t num_tiles,
                      const OptTensor& decode_seqs, int64_t num_decode, int64_t num_splits,
                      const OptTensor& scratch, int64_t force_kernel, const OptTensor& head_scale,
-                     const OptTensor& slopes, int64_t chunk, const OptTensor& sinks) {
+                     const OptTensor& slopes, int64_t chunk, const OptTensor& sinks, int64_t keep_first) {
   const AttnLib& lib = attn_lib(D);
   TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.stride(1) == 1 && q.size(1) >= num_heads * D,
               "paged_attention: q must be [T, >= heads*head_dim] with unit column stride");
@@ -369,6 +369,8 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   }
   TORCH_CHECK(chunk >= 0, "paged_attention: chunk must not be negative");
   a.chunk = (int)chunk;
+  TORCH_CHECK(keep_first >= 0 && !(keep_first > 0 && chunk > 0), "paged_attention: keep_first must not be negative, and not with chunks");
+  a.keep_first = (int)keep_first;
   if (sinks) {
     check_f32(*sinks, "sinks");
     TORCH_CHECK(sinks->numel() == num_heads, "paged_attention: sinks needs one value per head");
@@ -471,21 +473,29 @@ void latent_write(const Tensor& proj, int64_t col0, int64_t R, const Tensor& wei
 }
 
 // out[t, h, :] = w[h] . a[t, col0 + h*K : col0 + (h+1)*K]     w [H, N, K], out [T, H*N]
-void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out, int64_t kind) {
+const float* opt_f32(const OptTensor& t, int64_t n, const char* what);
+
+// a_head_cols / out_head_cols (0: K / N): columns from one head to the next in a and in out; a head's
+// result may be the first N columns of a wider slot of out.
+void head_linear(const Tensor& a, int64_t col0, const Tensor& w, Tensor& out, int64_t kind, int64_t a_head_cols,
+                 int64_t out_head_cols) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_cuda(out, "out");
   TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && out.dim() == 2, "head_linear: need a [T, >= H*K], w [H, N, K], out [T, H*N]");
   const int64_t H = w.size(0), N = w.size(1), K = w.size(2);
-  TORCH_CHECK(col0 >= 0 && col0 + H * K <= a.size(1) && out.size(0) == a.size(0) && out.size(1) == H * N,
+  const int64_t ah = a_head_cols > 0 ? a_head_cols : K, oh = out_head_cols > 0 ? out_head_cols : N;
+  TORCH_CHECK(ah >= K && oh >= N && col0 >= 0 && col0 + (H - 1) * ah + K <= a.size(1) && out.size(0) == a.size(0) &&
+                  out.size(1) == H * oh,
               "head_linear: shapes disagree");
   done(lse_head_linear(a.data_ptr(), out_code(a, "a"), a.size(1), col0, w.data_ptr(), out_code(w, "w"),
-                       out.data_ptr(), out_code(out, "out"), (int)a.size(0), (int)H, (int)N, (int)K, (int)kind, stream()),
+                       out.data_ptr(), out_code(out, "out"), (int)a.size(0), (int)H, (int)N, (int)K, (int)kind, stream(),
+                       ah, oh, out.size(1)),
        "head_linear");
 }
 
 void moe_route(const Tensor& h, const Tensor& router, int64_t E, int64_t top, Tensor& idx, Tensor& wts,
-               const OptTensor& gate) {
+               const OptTensor& gate, const OptTensor& bias, int64_t mode) {
   check_cuda(h, "h");
   check_f32(router, "router");
   check_i32(idx, "idx");
@@ -502,7 +512,8 @@ void moe_route(const Tensor& h, const Tensor& router, int64_t E, int64_t top, Te
     g = gate->data_ptr<float>();
   }
   done(lse_moe_route(h.data_ptr(), out_code(h, "h"), router.data_ptr<float>(), (int)T, (int)W, (int)E,
-                     has_gate, (int)top, idx.data_ptr<int>(), wts.data_ptr<float>(), g, stream()),
+                     has_gate, (int)top, idx.data_ptr<int>(), wts.data_ptr<float>(), g, stream(),
+                     opt_f32(bias, E, "router bias"), (int)mode),
        "moe_route");
 }
 
@@ -575,7 +586,7 @@ void expert_linear(const Tensor& a, const Tensor& w, Tensor& out, const Tensor& 
 }
 
 void moe_combine(const Tensor& y, const Tensor& work, int64_t E, int64_t top, const OptTensor& shared_out,
-                 const OptTensor& gate, Tensor& out, bool accumulate) {
+                 const OptTensor& gate, Tensor& out, bool accumulate, const OptTensor& wts) {
   check_f32(y, "y");
   check_i32(work, "work");
   check_f32(out, "out");
@@ -584,14 +595,16 @@ void moe_combine(const Tensor& y, const Tensor& work, int64_t E, int64_t top, co
   const float *sp = nullptr, *gp = nullptr;
   if (shared_out) {
     check_f32(*shared_out, "shared_out");
-    TORCH_CHECK(gate.has_value() && shared_out->sizes() == out.sizes(), "moe_combine: shared_out needs a gate and out's shape");
-    check_f32(*gate, "gate");
-    TORCH_CHECK(gate->numel() == T, "moe_combine: gate must be [T]");
+    TORCH_CHECK(shared_out->sizes() == out.sizes(), "moe_combine: shared_out needs out's shape");
     sp = shared_out->data_ptr<float>();
-    gp = gate->data_ptr<float>();
+    if (gate) {
+      check_f32(*gate, "gate");
+      TORCH_CHECK(gate->numel() == T, "moe_combine: gate must be [T]");
+      gp = gate->data_ptr<float>();
+    }
   }
   done(lse_moe_combine(y.data_ptr<float>(), work.data_ptr<int>() + E + 1 + n, (int)top, sp, gp,
-                       out.data_ptr<float>(), accumulate ? 1 : 0, (int)T, (int)W, stream()),
+                       out.data_ptr<float>(), accumulate ? 1 : 0, (int)T, (int)W, stream(), opt_f32(wts, n, "experts' weights")),
        "moe_combine");
 }
 
@@ -708,7 +721,7 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
   check_i32(token_seq, "token_seq");
   check_i32(block_tables, "block_tables");
   const int64_t heads = nq + nk + (v_from_k ? 0 : nk);
-  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == heads * D, "norm_rope_kv_write: qkv width");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) >= heads * D, "norm_rope_kv_write: qkv width");
   TORCH_CHECK(D > 0 && D <= 256, "norm_rope_kv_write: head size must be at most 256");
   const int64_t T = qkv.size(0);
   TORCH_CHECK(q_out.dim() == 2 && q_out.size(0) == T && q_out.size(1) == nq * D, "norm_rope_kv_write: q_out shape");
@@ -739,7 +752,7 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
                               (float)eps, positions.data_ptr<int>(), token_seq.data_ptr<int>(),
                               cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, kp, vp,
                               block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens,
-                              (int)norm_dim, stream()),
+                              (int)norm_dim, stream(), qkv.size(1)),
        "norm_rope_kv_write");
 }
 
@@ -975,6 +988,112 @@ void ban_tokens(Tensor& logits, const Tensor& row, const Tensor& token) {
 
 }  // namespace
 
+// ---- latent attention with a rotated key part, gates, plain activations (rotary_latent.cu) ----
+// proj [T, stride]: columns q_col0 .. +Rq are the query latent (Rq = q_weight's size; no q_weight:
+// none), columns kv_col0 .. +R the key/value latent and the Dr columns behind them the key part
+// that is turned by the position (R = kv_weight's size; no kv_weight: the layer writes no rows).
+void latent_rope_write(const Tensor& proj, int64_t q_col0, const OptTensor& q_weight, const OptTensor& cq,
+                       int64_t kv_col0, const OptTensor& kv_weight, int64_t Dr, int64_t rot, double eps,
+                       const OptTensor& cos, const OptTensor& sin, const OptTensor& pages, const Tensor& positions,
+                       const Tensor& token_seq, const Tensor& block_tables) {
+  check_cuda(proj, "proj");
+  check_i32(positions, "positions");
+  check_i32(token_seq, "token_seq");
+  check_i32(block_tables, "block_tables");
+  TORCH_CHECK(proj.dim() == 2 && block_tables.dim() == 2, "latent_rope_write: proj and block_tables are matrices");
+  const int64_t T = proj.size(0);
+  TORCH_CHECK(positions.numel() >= T && token_seq.numel() >= T, "latent_rope_write: the batch arrays are too short");
+  int64_t Rq = 0, R = 0, Rp = 0, page_tokens = 1;
+  int dtype = -1;
+  void *cq_ptr = nullptr, *pages_ptr = nullptr;
+  if (q_weight) {
+    check_f32(*q_weight, "q_weight");
+    Rq = q_weight->numel();
+    TORCH_CHECK(cq.has_value(), "latent_rope_write: a query latent needs its output");
+    check_cuda(*cq, "cq");
+    TORCH_CHECK(cq->dim() == 2 && cq->size(0) == T && cq->size(1) == Rq && q_col0 >= 0 && q_col0 + Rq <= proj.size(1),
+                "latent_rope_write: cq must be [T, query rank] and its columns lie in proj");
+    dtype = out_code(*cq, "cq");
+    cq_ptr = cq->data_ptr();
+  }
+  if (kv_weight) {
+    check_f32(*kv_weight, "kv_weight");
+    R = kv_weight->numel();
+    TORCH_CHECK(pages.has_value(), "latent_rope_write: a key/value latent needs its pages");
+    check_cuda(*pages, "pages");
+    TORCH_CHECK(pages->dim() == 4 && pages->size(1) == 1 && pages->size(3) >= R + Dr,
+                "latent_rope_write: pages must be [pages, 1, page_tokens, >= rank + rotated dims]");
+    TORCH_CHECK(kv_col0 >= 0 && Dr >= 0 && kv_col0 + R + Dr <= proj.size(1), "latent_rope_write: columns outside proj");
+    TORCH_CHECK(dtype < 0 || dtype == out_code(*pages, "pages"), "latent_rope_write: cq and pages must share a dtype");
+    dtype = out_code(*pages, "pages");
+    pages_ptr = pages->data_ptr();
+    Rp = pages->size(3);
+    page_tokens = pages->size(2);
+    TORCH_CHECK(rot >= 0 && rot <= Dr && rot % 2 == 0, "latent_rope_write: rot must be even and at most the key part's size");
+    if (rot > 0) {
+      TORCH_CHECK(cos.has_value() && sin.has_value(), "latent_rope_write: rotation needs its tables");
+      check_f32(*cos, "cos");
+      check_f32(*sin, "sin");
+      TORCH_CHECK(cos->dim() == 2 && cos->size(1) == rot / 2 && sin->sizes() == cos->sizes(),
+                  "latent_rope_write: cos and sin must be [positions, rot / 2]");
+    }
+  }
+  TORCH_CHECK(dtype >= 0, "latent_rope_write: nothing to do");
+  done(lse_latent_rope_write(proj.data_ptr(), out_code(proj, "proj"), proj.size(1), (int)q_col0, (int)Rq,
+                             q_weight ? q_weight->data_ptr<float>() : nullptr, cq_ptr, (int)kv_col0, (int)R, (int)Dr,
+                             (int)rot, kv_weight ? kv_weight->data_ptr<float>() : nullptr, (float)eps,
+                             cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, pages_ptr,
+                             (int)Rp, dtype, positions.data_ptr<int>(), token_seq.data_ptr<int>(),
+                             block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens, (int)T, stream()),
+       "latent_rope_write");
+}
+
+// q [T, H * (D + Dr)] -> out [T, H * Rp]: dims R .. R + Dr of every head's slot (turned), zeros behind.
+void latent_query_rope(const Tensor& q, int64_t H, int64_t D, int64_t Dr, int64_t rot, const OptTensor& cos,
+                       const OptTensor& sin, const Tensor& positions, Tensor& out, int64_t R) {
+  check_cuda(q, "q");
+  check_cuda(out, "out");
+  check_i32(positions, "positions");
+  TORCH_CHECK(q.dim() == 2 && out.dim() == 2 && H > 0 && q.size(1) == H * (D + Dr) && out.size(0) == q.size(0) &&
+                  out.size(1) % H == 0 && out.scalar_type() == q.scalar_type() && positions.numel() >= q.size(0),
+              "latent_query_rope: q must be [T, H * (D + Dr)] and out [T, H * slot] of the same dtype");
+  const int64_t Rp = out.size(1) / H;
+  TORCH_CHECK(R >= 0 && R + Dr <= Rp && rot >= 0 && rot <= Dr && rot % 2 == 0, "latent_query_rope: sizes disagree");
+  if (rot > 0) {
+    TORCH_CHECK(cos.has_value() && sin.has_value(), "latent_query_rope: rotation needs its tables");
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 2 && cos->size(1) == rot / 2 && sin->sizes() == cos->sizes(),
+                "latent_query_rope: cos and sin must be [positions, rot / 2]");
+  }
+  done(lse_latent_query_rope(q.data_ptr(), out_code(q, "q"), (int)q.size(0), (int)H, (int)D, (int)Dr, (int)rot,
+                             cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr,
+                             positions.data_ptr<int>(), out.data_ptr(), (int)R, (int)Rp, stream()),
+       "latent_query_rope");
+}
+
+// o[t, i] *= sigmoid(g[t, col0 + i / group])
+void sigmoid_gate_mul(Tensor& o, const Tensor& g, int64_t col0, int64_t group) {
+  check_cuda(o, "o");
+  check_cuda(g, "g");
+  TORCH_CHECK(o.dim() == 2 && g.dim() == 2 && g.size(0) == o.size(0) && group > 0 && col0 >= 0 &&
+                  col0 + (o.size(1) + group - 1) / group <= g.size(1),
+              "sigmoid_gate_mul: the gate's columns lie outside g");
+  done(lse_sigmoid_gate_mul(o.data_ptr(), out_code(o, "o"), g.data_ptr(), out_code(g, "g"), g.size(1), (int)col0,
+                            (int)group, (int)o.size(0), (int)o.size(1), stream()),
+       "sigmoid_gate_mul");
+}
+
+// out = act(in) element by element; in may be fixed-point sums (int64), which are left zero
+void act_rows(const Tensor& in, Tensor& out, int64_t act) {
+  check_cuda(in, "in");
+  check_cuda(out, "out");
+  TORCH_CHECK(in.numel() == out.numel(), "act_rows: sizes differ");
+  const int in_code = in.scalar_type() == torch::kInt64 ? LSE_FIXED64 : out_code(in, "in");
+  done(lse_act_rows(in.data_ptr(), in_code, out.data_ptr(), out_code(out, "out"), in.numel(), (int)act, stream()),
+       "act_rows");
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding);
   m.def("add_rmsnorm", &add_rmsnorm);
@@ -995,17 +1114,24 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_tables"), py::arg("ctx_lens"), py::arg("cu_q"), py::arg("tiles"), py::arg("num_tiles"),
         py::arg("decode_seqs"), py::arg("num_decode"), py::arg("num_splits"), py::arg("scratch"),
         py::arg("force_kernel"), py::arg("head_scale"), py::arg("slopes"), py::arg("chunk"),
-        py::arg("sinks") = py::none());
+        py::arg("sinks") = py::none(), py::arg("keep_first") = 0);
   m.def("hashed_pair_add", &hashed_pair_add);
   m.def("sinusoid_add", &sinusoid_add);
   m.def("latent_write", &latent_write);
-  m.def("head_linear", &head_linear);
-  m.def("moe_route", &moe_route);
+  m.def("head_linear", &head_linear, py::arg("a"), py::arg("col0"), py::arg("w"), py::arg("out"), py::arg("kind"),
+        py::arg("a_head_cols") = 0, py::arg("out_head_cols") = 0);
+  m.def("moe_route", &moe_route, py::arg("h"), py::arg("router"), py::arg("num_experts"), py::arg("top"),
+        py::arg("idx"), py::arg("wts"), py::arg("gate"), py::arg("bias") = py::none(), py::arg("mode") = 0);
   m.def("moe_max_tiles", &moe_max_tiles);
   m.def("moe_tile_rows", &moe_tile_rows);
   m.def("moe_sort", &moe_sort);
   m.def("expert_linear", &expert_linear);
-  m.def("moe_combine", &moe_combine);
+  m.def("moe_combine", &moe_combine, py::arg("y"), py::arg("work"), py::arg("num_experts"), py::arg("top"),
+        py::arg("shared_out"), py::arg("gate"), py::arg("out"), py::arg("accumulate"), py::arg("wts") = py::none());
+  m.def("latent_rope_write", &latent_rope_write);
+  m.def("latent_query_rope", &latent_query_rope);
+  m.def("sigmoid_gate_mul", &sigmoid_gate_mul);
+  m.def("act_rows", &act_rows);
   m.def("cast_f32", &cast_f32);
   m.def("token_shift", &token_shift);
   m.def("rmsnorm_add", &rmsnorm_add);

@@ -149,7 +149,8 @@ int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, int T, int 
                            int v_from_k, const float* qw, const float* kw, float eps,
                            const int* positions, const int* token_seq, const float* cos,
                            const float* sin, void* k_pages, void* v_pages, const int* block_tables,
-                           int table_stride, int page_tokens, int norm_dim, cudaStream_t stream);
+                           int table_stride, int page_tokens, int norm_dim, cudaStream_t stream,
+                           long long row_stride = 0);  // of qkv, in elements (0: dense rows)
 
 // Linear attention with a decay per head, token by token in float32:
 //   S_t = decay[h] * S_{t-1} + k_t v_t^T,  out_t = S_t^T q_t
@@ -195,13 +196,18 @@ int lse_latent_write(const void* proj, int in_dtype, long long stride, int col0,
 // kind: 0 = CUDA cores; 1 = mma.sync tensor-core tiles; 2 = a kernel for few rows that streams the
 // weights once. 1 and 2 need bfloat16 a and w with K, a_stride and a_col0 multiples of 8 (else the
 // call is served as kind 0).
+// a_head_cols: columns between the heads of a (0: K); out_head_cols: columns between the heads of
+// out (0: N), out_stride its row length (0: H * out_head_cols): a head's result may be the first
+// part of a wider slot whose rest another kernel fills.
 int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0, const void* w,
                     int w_dtype, void* out, int out_dtype, int T, int H, int N, int K, int kind,
-                    cudaStream_t stream);
+                    cudaStream_t stream, long long a_head_cols = 0, long long out_head_cols = 0,
+                    long long out_stride = 0);
 
 // Routed experts. h [T, W]; router float32 [E (+1), W].
-//   lse_moe_route: scores = sigmoid(router . h); idx/wts [T, top] the top experts (largest score
-//     first, the lower index on a tie) and their scores; with has_gate, gate[t] = sigmoid(router[E] . h).
+//   lse_moe_route: z = router . h (+ bias); idx [T, top] the experts with the largest z (largest
+//     first, the lower index on a tie). mode 0: wts = sigmoid(z) of the chosen; mode 1: wts = the
+//     softmax over the chosen z alone. With has_gate, gate[t] = sigmoid(router[E] . h).
 //   lse_moe_sort: the n = T * top choices sorted by expert: offsets [E + 1], perm [n] (sorted row ->
 //     choice), pos_of [n] (choice -> sorted row), and tiles of at most lse_moe_tile_rows() rows of one
 //     expert each (tile_batch, tile_row0: room for n / tile_rows + E entries; num_tiles [1]);
@@ -210,10 +216,12 @@ int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_
 //     [rows, N]; arow(r) = a[a_rows[r] / a_div] * a_scale[a_rows[r]] (a_rows null: a[r], unscaled);
 //     w [E, N, K]. Launched for max_tiles tiles; tiles beyond *num_tiles do nothing. kind as above
 //     (kinds 1 and 2 multiply the float32 sums by a_scale, which is the same product).
-//   lse_moe_combine: out[t] (+)= sum_k y[pos_of[t*top + k]] (+ gate[t] * shared_out[t]).
+//   lse_moe_combine: out[t] (+)= sum_k wts[t*top + k] * y[pos_of[t*top + k]] (+ gate[t] * shared_out[t]);
+//     wts null: 1; gate null: 1.
 int lse_moe_tile_rows(void);
 int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E, int has_gate,
-                  int top, int* idx, float* wts, float* gate, cudaStream_t stream);
+                  int top, int* idx, float* wts, float* gate, cudaStream_t stream,
+                  const float* bias = nullptr, int mode = 0);
 int lse_moe_sort(const int* idx, int n, int E, int tile_rows, int* offsets, int* perm, int* pos_of,
                  int* tile_batch, int* tile_row0, int* num_tiles, cudaStream_t stream);
 // out[r] = a[perm[r] / top] for the n sorted rows (bfloat16, K a multiple of 8)
@@ -232,5 +240,32 @@ int lse_expert_linear(const void* a, int a_dtype, long long a_stride, const int*
                       int K, const int* offsets, const int* tile_batch, const int* tile_row0,
                       const int* num_tiles, int max_tiles, int kind, cudaStream_t stream);
 int lse_moe_combine(const float* y, const int* pos_of, int top, const float* shared_out,
-                    const float* gate, float* out, int accumulate, int T, int W, cudaStream_t stream);
+                    const float* gate, float* out, int accumulate, int T, int W, cudaStream_t stream,
+                    const float* wts = nullptr);
+
+// Latent attention with a rotated key part (rotary_latent.cu). cos/sin: float32 [positions, rot/2];
+// neighbouring dims (2i, 2i+1) are a pair; of a part's Dr dims the first rot are turned.
+//   lse_latent_rope_write: per row of proj (row length `stride`): if Rq > 0, columns q_col0 .. +Rq
+//     RMS-normed with q_weight into cq [T, Rq]; if R > 0, columns kv_col0 .. +R RMS-normed with
+//     kv_weight and the Dr columns behind them turned by the token's position, written as one row
+//     [R | Dr | zeros up to Rp] at the token's place of pages [pages, 1, page_tokens, Rp].
+//   lse_latent_query_rope: q [T, H, D + Dr]; out [T, H, Rp]: dims R .. R + Dr of every head take the
+//     head's last Dr query dims turned by the position, dims R + Dr .. Rp zeros; dims below R are
+//     not touched.
+//   lse_sigmoid_gate_mul: o[t, i] *= sigmoid(g[t * g_stride + col0 + i / group]) for i < N.
+//   lse_act_rows: out[i] = act(in[i]); act 0: relu(z)^2, 1: relu, 2: gelu_tanh, 3: silu. `in` may be
+//     fixed-point sums (LSE_FIXED64, bfloat16 out), which are left zero.
+int lse_latent_rope_write(const void* proj, int in_dtype, long long stride, int q_col0, int Rq,
+                          const float* q_weight, void* cq, int kv_col0, int R, int Dr, int rot,
+                          const float* kv_weight, float eps, const float* cos, const float* sin,
+                          void* pages, int Rp, int dtype, const int* positions, const int* token_seq,
+                          const int* block_tables, int table_stride, int page_tokens, int T,
+                          cudaStream_t stream);
+int lse_latent_query_rope(const void* q, int dtype, int T, int H, int D, int Dr, int rot,
+                          const float* cos, const float* sin, const int* positions, void* out, int R,
+                          int Rp, cudaStream_t stream);
+int lse_sigmoid_gate_mul(void* o, int dtype, const void* g, int g_dtype, long long g_stride, int col0,
+                         int group, int T, int N, cudaStream_t stream);
+int lse_act_rows(const void* in, int in_dtype, void* out, int dtype, long long total, int act,
+                 cudaStream_t stream);
 }

@@ -7,7 +7,8 @@
 //                     and scaled and whose weights are chosen per head (batched over heads) or per
 //                     tile (experts); each output element is one thread's in-order sum over k, so
 //                     a row's result does not depend on the batch it is in
-//   moe_route         sigmoid scores of a router, the top-k experts per token, a shared gate
+//   moe_route         a router's logits (+ bias), the top-k experts per token with sigmoid scores or
+//                     a softmax over the chosen logits, a shared gate
 //   moe_sort          tokens' expert choices sorted by expert, as tiles of rows for rows_gemm
 //   moe_combine       per token: the sum of its experts' rows (+ gate * shared expert), into x
 #include "common.cuh"
@@ -450,16 +451,17 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) rows_gemv_kernel(const RowsG
 // ------------------------------------------------------------------------------------ routing
 // One block of eight warps per token. Every router row is shared by the eight warps (warp w takes
 // the columns w * 32 + lane, + 256, ...); the warps' partial sums are added in the order of the
-// warps, so a score depends on nothing but the width. scores = sigmoid(router . h) in float32;
-// then the first warp picks the `top` largest (the lower index on a tie) with their scores. Row E
-// of the router, if there is one, is the shared expert's gate.
+// warps, so a score depends on nothing but the width. z = router . h (+ bias) in float32; then the
+// first warp picks the `top` largest (the lower index on a tie). Their weights: sigmoid(z) (mode 0;
+// the sigmoid is monotone, so the order is that of z) or the softmax over the chosen z alone
+// (mode 1). Row E of the router, if there is one, is the shared expert's gate.
 constexpr int ROUTE_WARPS = 8;
 
 template <typename TH>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int W, int E,
                  int has_gate, int top, int* __restrict__ idx, float* __restrict__ wts,
-                 float* __restrict__ gate) {
+                 float* __restrict__ gate, const float* __restrict__ bias, int mode) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
   extern __shared__ float s[];  // [E + 1] scores, then [E + 1][ROUTE_WARPS] partial sums
@@ -480,17 +482,17 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
     float d = 0.f;
 #pragma unroll
     for (int w = 0; w < ROUTE_WARPS; ++w) d += part[e * ROUTE_WARPS + w];
-    const float sg = 1.f / (1.f + expf(-d));
-    if (e < E) s[e] = sg;
-    else gate[t] = sg;
+    if (e < E) s[e] = d + (bias ? bias[e] : 0.f);
+    else gate[t] = 1.f / (1.f + expf(-d));
   }
   __syncthreads();
   if (warp != 0) return;
+  float first = 0.f, total = 0.f;  // mode 1: the largest chosen logit, the sum of the exponentials
   for (int k = 0; k < top; ++k) {
-    float best = -2.f;
+    float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
-      if (s[e] > best) {
+      if (s[e] > best || (bi == 0x7fffffff && s[e] == best)) {
         best = s[e];
         bi = e;
       }
@@ -503,13 +505,19 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, int
         bi = oi;
       }
     }
+    if (bi == 0x7fffffff) bi = 0;  // only if every logit left is NaN
+    if (k == 0) first = best;
+    const float wk = mode == 0 ? 1.f / (1.f + expf(-best)) : expf(best - first);
+    total += wk;
     if (lane == 0) {
       idx[t * top + k] = bi;
-      wts[t * top + k] = best;
-      s[bi] = -1.f;  // taken (a sigmoid is never negative)
+      wts[t * top + k] = wk;
+      s[bi] = -INFINITY;  // taken
     }
     __syncwarp();
   }
+  if (mode == 1)
+    for (int k = lane; k < top; k += 32) wts[t * top + k] /= total;
 }
 
 // One block. n choices idx[i] in [0, E): offsets[e] .. offsets[e+1] are expert e's rows in the
@@ -574,28 +582,30 @@ moe_gather_rows_kernel(const bf16* __restrict__ a, const int* __restrict__ perm,
   store16(out + (size_t)r * K + c * 8, load16(a + (size_t)(perm[r] / top) * K + c * 8));
 }
 
-// x[t] (or out[t]) (+)= sum_k y[pos_of[t * top + k]] + gate[t] * shared[t]; a block per token and
+// x[t] (or out[t]) (+)= sum_k wts[t * top + k] * y[pos_of[t * top + k]] + gate[t] * shared[t] (a
+// null wts or gate counts as ones); a block per token and
 // slice of 512 columns, four columns per thread (the experts' rows are added in the order k = 0, 1, ...)
 constexpr int COMBINE_SLICE = 512;
 
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, int top,
                    const float* __restrict__ shared_out, const float* __restrict__ gate,
-                   float* __restrict__ out, int accumulate, int W) {
+                   float* __restrict__ out, int accumulate, int W, const float* __restrict__ wts) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
   const int t = blockIdx.x;
-  const float g = gate ? gate[t] : 0.f;
+  const float g = gate ? gate[t] : 1.f;
   const int i0 = blockIdx.y * COMBINE_SLICE + threadIdx.x;
   float v[COMBINE_SLICE / 128];
 #pragma unroll
   for (int j = 0; j < COMBINE_SLICE / 128; ++j) v[j] = 0.f;
   for (int k = 0; k < top; ++k) {
     const float* row = y + (size_t)pos_of[(size_t)t * top + k] * W;
+    const float wk = wts ? wts[(size_t)t * top + k] : 1.f;
 #pragma unroll
     for (int j = 0; j < COMBINE_SLICE / 128; ++j) {
       const int i = i0 + j * 128;
-      if (i < W) v[j] += row[i];
+      if (i < W) v[j] = fmaf(wk, row[i], v[j]);
     }
   }
 #pragma unroll
@@ -692,13 +702,18 @@ static int launch_rows_gemm(const RowsGemm& g, int a_dtype, int w_dtype, int out
 
 extern "C" int lse_head_linear(const void* a, int a_dtype, long long a_stride, long long a_col0,
                                const void* w, int w_dtype, void* out, int out_dtype, int T, int H,
-                               int N, int K, int kind, cudaStream_t stream) {
+                               int N, int K, int kind, cudaStream_t stream, long long a_head_cols,
+                               long long out_head_cols, long long out_stride) {
   if (T <= 0 || H <= 0 || N <= 0) return LSE_OK;
   if (K <= 0) return LSE_BAD_ARGUMENT;
+  if (a_head_cols <= 0) a_head_cols = K;
+  if (out_head_cols <= 0) out_head_cols = N;
+  if (out_stride <= 0) out_stride = (long long)H * out_head_cols;
+  if (a_head_cols < K || out_head_cols < N) return LSE_BAD_ARGUMENT;
   RowsGemm g = {};
-  g.a = a; g.a_stride = a_stride; g.a_col0 = a_col0; g.a_batch_cols = K; g.a_div = 1;
+  g.a = a; g.a_stride = a_stride; g.a_col0 = a_col0; g.a_batch_cols = a_head_cols; g.a_div = 1;
   g.w = w; g.w_batch_stride = (long long)N * K;
-  g.out = out; g.out_stride = (long long)H * N; g.out_batch_cols = N;
+  g.out = out; g.out_stride = out_stride; g.out_batch_cols = out_head_cols;
   g.T = T; g.N = N; g.K = K;
   return launch_rows_gemm(g, a_dtype, w_dtype, out_dtype, dim3((N + BN - 1) / BN, (T + BM - 1) / BM, H), stream,
                           kind);
@@ -724,16 +739,16 @@ extern "C" int lse_expert_linear(const void* a, int a_dtype, long long a_stride,
 
 extern "C" int lse_moe_route(const void* h, int h_dtype, const float* router, int T, int W, int E,
                              int has_gate, int top, int* idx, float* wts, float* gate,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const float* bias, int mode) {
   if (T <= 0) return LSE_OK;
-  if (E <= 0 || top <= 0 || top > E || E > 1024 || (has_gate && !gate)) return LSE_BAD_ARGUMENT;
+  if (E <= 0 || top <= 0 || top > E || E > 1024 || (has_gate && !gate) || mode < 0 || mode > 1) return LSE_BAD_ARGUMENT;
   const size_t smem = (size_t)(E + 1) * (1 + ROUTE_WARPS) * sizeof(float);
   if (h_dtype == LSE_F32)
     launch(moe_route_kernel<float>, T, ROUTE_WARPS * 32, smem, stream, (const float*)h, router, W, E, has_gate, top,
-                                                                   idx, wts, gate);
+                                                                   idx, wts, gate, bias, mode);
   else if (h_dtype == LSE_BF16)
     launch(moe_route_kernel<bf16>, T, ROUTE_WARPS * 32, smem, stream, (const bf16*)h, router, W, E, has_gate, top,
-                                                                  idx, wts, gate);
+                                                                  idx, wts, gate, bias, mode);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
@@ -761,10 +776,9 @@ extern "C" int lse_moe_gather_rows(const void* a, const int* perm, int top, void
 
 extern "C" int lse_moe_combine(const float* y, const int* pos_of, int top, const float* shared_out,
                                const float* gate, float* out, int accumulate, int T, int W,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const float* wts) {
   if (T <= 0) return LSE_OK;
-  if (shared_out && !gate) return LSE_BAD_ARGUMENT;
   launch(moe_combine_kernel, dim3(T, (W + COMBINE_SLICE - 1) / COMBINE_SLICE), 128, 0, stream, y, pos_of, top,
-         shared_out, gate, out, accumulate, W);
+         shared_out, gate, out, accumulate, W, wts);
   return LSE_CHECK_LAUNCH();
 }

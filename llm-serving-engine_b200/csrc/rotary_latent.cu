@@ -1,0 +1,230 @@
+// Kernels of latent attention whose keys carry a rotated part, of output gates and of plain
+// (ungated) activations.
+//
+//   latent_rope_write   per token: the key/value latent RMS-normed and, behind it, the key part
+//                       that all heads share, turned by the token's position (neighbouring dims
+//                       are a pair), both into the token's row of its page; and the query latent
+//                       RMS-normed into a dense tensor
+//   latent_query_rope   per token and head: the head's rotated query dims turned by the position
+//                       and placed behind the head's latent-space query; the row's padding zeroed
+//   sigmoid_gate_mul    o[t, i] *= sigmoid(g[t, col0 + i / group])
+//   act_rows            out = act(in) element by element (act: the square of relu, relu, gelu_tanh, silu)
+//
+// Norms, angles, rotations, sigmoids and activations are float32 arithmetic whatever the types
+// of the tensors are.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lse {
+
+// Turn the pair (u, v) = (x[2i], x[2i+1]) by the angle of (pos, i): cos/sin [positions, rot/2].
+__device__ __forceinline__ float rotated_neighbour(const float* x, int i, int rot, const float* cr,
+                                                   const float* sr) {
+  if (i >= rot) return x[i];
+  const int p = i >> 1;
+  return (i & 1) ? x[i] * cr[p] + x[i - 1] * sr[p] : x[i] * cr[p] - x[i + 1] * sr[p];
+}
+
+constexpr int LRW_THREADS = 128;
+
+// One block per token. proj row: [.. q latent at q_col0 (Rq dims) .. kv latent at kv_col0 (R dims)
+// followed by the shared key part (Dr dims) ..]. Rq = 0: no query latent; R = 0: no key/value side
+// (a layer that reads rows another layer wrote).
+template <typename TIn, typename T>
+__global__ void __launch_bounds__(LRW_THREADS)
+latent_rope_write_kernel(const TIn* __restrict__ proj, long long stride, int q_col0, int Rq,
+                         const float* __restrict__ q_weight, T* __restrict__ cq, int kv_col0, int R,
+                         int Dr, int rot, const float* __restrict__ kv_weight, float eps,
+                         const float* __restrict__ cos, const float* __restrict__ sin,
+                         T* __restrict__ pages, int Rp, const int* __restrict__ positions,
+                         const int* __restrict__ token_seq, const int* __restrict__ block_tables,
+                         int table_stride, int page_tokens) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  __shared__ float red[32];
+  extern __shared__ float kr[];  // [Dr] the key part as projected
+  const int t = blockIdx.x;
+  const TIn* row = proj + (size_t)t * stride;
+  if (Rq > 0) {
+    const TIn* src = row + q_col0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < Rq; i += LRW_THREADS) {
+      const float v = Num<TIn>::to_float(src[i]);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float r = rsqrtf(ss / (float)Rq + eps);
+    T* dst = cq + (size_t)t * Rq;
+    for (int i = threadIdx.x; i < Rq; i += LRW_THREADS)
+      dst[i] = Num<T>::from_float(Num<TIn>::to_float(src[i]) * r * q_weight[i]);
+  }
+  if (R <= 0) return;
+  const TIn* src = row + kv_col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < R; i += LRW_THREADS) {
+    const float v = Num<TIn>::to_float(src[i]);
+    ss += v * v;
+  }
+  for (int i = threadIdx.x; i < Dr; i += LRW_THREADS) kr[i] = Num<TIn>::to_float(src[R + i]);
+  ss = block_sum(ss, red);  // its barriers also publish kr
+  const float r = rsqrtf(ss / (float)R + eps);
+  const int pos = positions[t];
+  const int page = block_tables[(size_t)token_seq[t] * table_stride + pos / page_tokens];
+  T* dst = pages + ((size_t)page * page_tokens + pos % page_tokens) * Rp;
+  const float* cr = cos + (size_t)pos * (rot / 2);
+  const float* sr = sin + (size_t)pos * (rot / 2);
+  for (int i = threadIdx.x; i < Rp; i += LRW_THREADS) {
+    float v = 0.f;
+    if (i < R) v = Num<TIn>::to_float(src[i]) * r * kv_weight[i];
+    else if (i < R + Dr) v = rotated_neighbour(kr, i - R, rot, cr, sr);
+    dst[i] = Num<T>::from_float(v);
+  }
+}
+
+// One warp per (token, head). q row: heads of (D + Dr) dims, the last Dr to be rotated. out row:
+// heads of Rp dims; dims [R, R + Dr) receive the rotated part, [R + Dr, Rp) zeros. Dims [0, R) are
+// written by the per-head product that runs beside this kernel.
+constexpr int LQR_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(LQR_WARPS * 32)
+latent_query_rope_kernel(const T* __restrict__ q, int H, int D, int Dr, int rot,
+                         const float* __restrict__ cos, const float* __restrict__ sin,
+                         const int* __restrict__ positions, T* __restrict__ out, int R, int Rp) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  extern __shared__ float qr_all[];  // [LQR_WARPS][Dr]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, h = blockIdx.y * LQR_WARPS + warp;
+  if (h >= H) return;
+  float* qr = qr_all + warp * Dr;
+  const T* src = q + ((size_t)t * H + h) * (D + Dr) + D;
+  for (int i = lane; i < Dr; i += 32) qr[i] = Num<T>::to_float(src[i]);
+  __syncwarp();
+  const int pos = positions[t];
+  const float* cr = cos + (size_t)pos * (rot / 2);
+  const float* sr = sin + (size_t)pos * (rot / 2);
+  T* dst = out + ((size_t)t * H + h) * Rp + R;
+  for (int i = lane; i < Rp - R; i += 32)
+    dst[i] = Num<T>::from_float(i < Dr ? rotated_neighbour(qr, i, rot, cr, sr) : 0.f);
+}
+
+template <typename T, typename TG>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_mul_kernel(T* __restrict__ o, const TG* __restrict__ g, long long g_stride, int col0,
+                        int group, int N, long long total) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / N;
+  const int c = (int)(i - t * N);
+  const float z = Num<TG>::to_float(g[t * g_stride + col0 + c / group]);
+  o[i] = Num<T>::from_float(Num<T>::to_float(o[i]) / (1.f + expf(-z)));
+}
+
+__device__ __forceinline__ float plain_activation(float z, int act) {
+  switch (act) {
+    case 0: {  // the square of relu
+      const float r = fmaxf(z, 0.f);
+      return r * r;
+    }
+    case 1: return fmaxf(z, 0.f);
+    case 2: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    default: return z / (1.f + expf(-z));
+  }
+}
+
+template <typename TIn, typename T>
+__global__ void __launch_bounds__(256)
+act_rows_kernel(const TIn* __restrict__ in, T* __restrict__ out, long long total, int act, int clear) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  out[i] = Num<T>::from_float(plain_activation(Num<TIn>::to_float(in[i]), act));
+  if (clear) const_cast<TIn*>(in)[i] = Num<TIn>::from_float(0.f);  // fixed-point sums are left zero
+}
+
+}  // namespace lse
+
+using namespace lse;
+
+#define LSE_CHECK_LAUNCH() (cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
+
+extern "C" int lse_latent_rope_write(const void* proj, int in_dtype, long long stride, int q_col0, int Rq,
+                                     const float* q_weight, void* cq, int kv_col0, int R, int Dr, int rot,
+                                     const float* kv_weight, float eps, const float* cos, const float* sin,
+                                     void* pages, int Rp, int dtype, const int* positions,
+                                     const int* token_seq, const int* block_tables, int table_stride,
+                                     int page_tokens, int T, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (Rq < 0 || R < 0 || (Rq == 0 && R == 0)) return LSE_BAD_ARGUMENT;
+  if (Rq > 0 && (!q_weight || !cq)) return LSE_BAD_ARGUMENT;
+  if (R > 0 && (Dr < 0 || rot < 0 || rot > Dr || rot % 2 || Rp < R + Dr || page_tokens <= 0 || !pages ||
+                !kv_weight || (rot > 0 && (!cos || !sin))))
+    return LSE_BAD_ARGUMENT;
+  const size_t smem = (size_t)(Dr > 0 ? Dr : 1) * sizeof(float);
+#define LSE_LRW(TIn, T_) \
+  launch(latent_rope_write_kernel<TIn, T_>, T, LRW_THREADS, smem, stream, (const TIn*)proj, stride, q_col0, Rq, \
+         q_weight, (T_*)cq, kv_col0, R, Dr, rot, kv_weight, eps, cos, sin, (T_*)pages, Rp, positions, token_seq, \
+         block_tables, table_stride, page_tokens)
+  if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_LRW(float, float);
+  else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_LRW(float, bf16);
+  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_LRW(bf16, bf16);
+  else return LSE_BAD_ARGUMENT;
+#undef LSE_LRW
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_latent_query_rope(const void* q, int dtype, int T, int H, int D, int Dr, int rot,
+                                     const float* cos, const float* sin, const int* positions, void* out,
+                                     int R, int Rp, cudaStream_t stream) {
+  if (T <= 0 || H <= 0) return LSE_OK;
+  if (D < 0 || Dr < 0 || rot < 0 || rot > Dr || rot % 2 || Rp < R + Dr || (rot > 0 && (!cos || !sin)))
+    return LSE_BAD_ARGUMENT;
+  if (Rp == R) return LSE_OK;
+  const dim3 grid(T, (H + LQR_WARPS - 1) / LQR_WARPS);
+  if (grid.y > 65535) return LSE_BAD_ARGUMENT;
+  const size_t smem = (size_t)LQR_WARPS * (Dr > 0 ? Dr : 1) * sizeof(float);
+  if (dtype == LSE_F32)
+    launch(latent_query_rope_kernel<float>, grid, LQR_WARPS * 32, smem, stream, (const float*)q, H, D, Dr, rot, cos,
+           sin, positions, (float*)out, R, Rp);
+  else if (dtype == LSE_BF16)
+    launch(latent_query_rope_kernel<bf16>, grid, LQR_WARPS * 32, smem, stream, (const bf16*)q, H, D, Dr, rot, cos,
+           sin, positions, (bf16*)out, R, Rp);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_sigmoid_gate_mul(void* o, int dtype, const void* g, int g_dtype, long long g_stride,
+                                    int col0, int group, int T, int N, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return LSE_OK;
+  if (group <= 0 || col0 < 0) return LSE_BAD_ARGUMENT;
+  const long long total = (long long)T * N;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+#define LSE_SGM(T_, TG) \
+  launch(sigmoid_gate_mul_kernel<T_, TG>, blocks, 256, 0, stream, (T_*)o, (const TG*)g, g_stride, col0, group, N, total)
+  if (dtype == LSE_F32 && g_dtype == LSE_F32) LSE_SGM(float, float);
+  else if (dtype == LSE_BF16 && g_dtype == LSE_F32) LSE_SGM(bf16, float);
+  else if (dtype == LSE_BF16 && g_dtype == LSE_BF16) LSE_SGM(bf16, bf16);
+  else return LSE_BAD_ARGUMENT;
+#undef LSE_SGM
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_act_rows(const void* in, int in_dtype, void* out, int dtype, long long total, int act,
+                            cudaStream_t stream) {
+  if (total <= 0) return LSE_OK;
+  if (act < 0 || act > 3) return LSE_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+#define LSE_ACT(TIn, T_, clear) \
+  launch(act_rows_kernel<TIn, T_>, blocks, 256, 0, stream, (const TIn*)in, (T_*)out, total, act, clear)
+  if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ACT(float, float, 0);
+  else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ACT(float, bf16, 0);
+  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ACT(bf16, bf16, 0);
+  else if (in_dtype == LSE_FIXED64 && dtype == LSE_BF16) LSE_ACT(fixed64, bf16, 1);
+  else return LSE_BAD_ARGUMENT;
+#undef LSE_ACT
+  return LSE_CHECK_LAUNCH();
+}

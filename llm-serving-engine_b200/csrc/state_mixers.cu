@@ -196,7 +196,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
                                           const float* __restrict__ cos, const float* __restrict__ sin,
                                           T* __restrict__ k_pages, T* __restrict__ v_pages,
                                           const int* __restrict__ block_tables, int table_stride,
-                                          int page_tokens, int norm_dim) {
+                                          int page_tokens, int norm_dim, long long row_stride) {
   __shared__ float buf[NRW_WARPS][256];
   pdl_trigger();
   pdl_wait();
@@ -205,7 +205,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
   const int nv = v_from_k ? 0 : nk;
   const int hs = blockIdx.y * NRW_WARPS + warp;
   if (hs >= nq + nk + nv) return;
-  const float* src = qkv + (size_t)t * (nq + nk + nv) * D + (size_t)hs * D;
+  const float* src = qkv + (size_t)t * row_stride + (size_t)hs * D;
   const int pos = positions[t];
   size_t page_base = 0;
   if (hs >= nq) {
@@ -672,7 +672,8 @@ extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, 
                                       const int* positions, const int* token_seq, const float* cos,
                                       const float* sin, void* k_pages, void* v_pages,
                                       const int* block_tables, int table_stride, int page_tokens,
-                                      int norm_dim, cudaStream_t stream) {
+                                      int norm_dim, cudaStream_t stream, long long row_stride) {
+  if (row_stride <= 0) row_stride = (long long)(nq + nk + (v_from_k ? 0 : nk)) * D;
   if (T <= 0) return LSE_OK;
   if (D <= 0 || D > 256 || (cos && D % 2) || (!qw != !kw) || (!cos != !sin) || (!k_pages != !v_pages) ||
       page_tokens <= 0)
@@ -683,11 +684,11 @@ extern "C" int lse_norm_rope_kv_write(const float* qkv, void* q_out, int dtype, 
   if (dtype == LSE_BF16)
     launch(norm_rope_kv_write_kernel<bf16>, grid, NRW_WARPS * 32, 0, stream, qkv, (bf16*)q_out, nq, nk, D,
            v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
-           block_tables, table_stride, page_tokens, norm_dim);
+           block_tables, table_stride, page_tokens, norm_dim, row_stride);
   else if (dtype == LSE_F32)
     launch(norm_rope_kv_write_kernel<float>, grid, NRW_WARPS * 32, 0, stream, qkv, (float*)q_out, nq, nk, D,
            v_from_k, qw, kw, eps, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
-           block_tables, table_stride, page_tokens, norm_dim);
+           block_tables, table_stride, page_tokens, norm_dim, row_stride);
   else return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
 }

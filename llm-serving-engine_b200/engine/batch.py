@@ -132,8 +132,10 @@ def build_host_step(entries: Sequence[StepEntry], manager, vocab_size: int, max_
         if spec.window > 0:
             # pages that the window has passed are given back (-1) and never read: the kernels start
             # at the page of key ``start - window + 1``; all later entries must be pages held
+            # (and at the pages of the first tokens that the group keeps readable, which are held too)
             first_page = np.maximum(0, starts - spec.window + 1) // spec.page_tokens
             live = np.arange(t.shape[1])[None, :] >= first_page[:, None]
+            live |= np.arange(t.shape[1])[None, :] < spec.kept_pages
             bad = ((t < 0) & live).any(axis=1)
             np.maximum(t, 0, out=t)
         else:

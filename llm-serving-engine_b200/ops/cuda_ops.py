@@ -410,10 +410,11 @@ class CudaOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan, head_scale=None, slopes=None,
-                        chunk=0, sinks=None):
+                        chunk=0, sinks=None, keep_first=0):
         """``head_scale`` / ``slopes`` (float32 ``[heads]``) and ``chunk``: a factor per head on the
         score, ``slope_h * (i - j)`` taken off it, and keys limited to the query's chunk. ``sinks``
-        (float32 ``[heads]``): ``exp(sink_h)`` joins the softmax's denominator."""
+        (float32 ``[heads]``): ``exp(sink_h)`` joins the softmax's denominator. ``keep_first``: with
+        a window, the sequence's first ``keep_first`` keys stay visible beside the window's."""
         out = torch.empty(q.shape[0], num_heads * head_dim, dtype=q.dtype, device=q.device)
         n_tiles = int(plan["tiles"].shape[0])
         n_dec = int(plan["decode_seqs"].shape[0])
@@ -428,7 +429,7 @@ class CudaOps:
             int(window), block_tables, step.ctx_lens, step.cu_q,
             plan["tiles"] if n_tiles else None, n_tiles,
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
-            self.attention_kernel, head_scale, slopes, int(chunk), sinks,
+            self.attention_kernel, head_scale, slopes, int(chunk), sinks, int(keep_first) if window else 0,
         )
         self.launches += (1 if n_tiles else 0) + (1 if n_dec else 0)
         return out
@@ -438,7 +439,8 @@ class CudaOps:
                            block_tables, page_tokens, out_dtype, norm_dim=None):
         """Head-wise RMS norm of q and k (if weights are given), rotation (if tables are given),
         key/value page write; returns the queries ``[T, heads * head_dim]`` in ``out_dtype``.
-        ``qkv`` is the float32 projection; with ``values_are_keys`` it has no value heads and a
+        ``qkv`` is the float32 projection (its rows may be wider than q, k and v: what lies behind
+        them is not read); with ``values_are_keys`` it has no value heads and a
         token's value is its key as projected. ``norm_dim``: the number of dims the mean of the
         norm is taken over, when the trailing dims of a head are zero padding."""
         q = torch.empty(qkv.shape[0], num_heads * head_dim, dtype=out_dtype, device=qkv.device)
@@ -478,24 +480,84 @@ class CudaOps:
             return 0
         return 2 if rows <= few else 1
 
-    def head_linear(self, a, col0, w, out_dtype, kind=None):
+    def head_linear(self, a, col0, w, out_dtype, kind=None, a_head_cols=0, out_head_cols=0):
         """A product per head: ``out[t, h] = w[h] @ a[t, col0 + h*K : col0 + (h+1)*K]`` for ``w``
-        ``[H, N, K]``; returns ``[T, H*N]``. ``kind`` forces a kernel (tests compare them)."""
-        out = torch.empty(a.shape[0], w.shape[0] * w.shape[1], dtype=out_dtype, device=a.device)
+        ``[H, N, K]``; returns ``[T, H*N]``. ``kind`` forces a kernel (tests compare them).
+        ``a_head_cols`` (default K): columns from one head to the next in ``a``, whose heads may
+        carry more than the K columns that are read. ``out_head_cols`` (default N): the result is
+        ``[T, H * out_head_cols]`` and a head's product fills the first N columns of its slot; the
+        rest is left for the caller to fill."""
+        out = torch.empty(a.shape[0], w.shape[0] * (out_head_cols or w.shape[1]), dtype=out_dtype, device=a.device)
         kind = self._rows_kernel(a, w, a.shape[0], self.skinny_max_rows) if kind is None else kind
-        self.ext.head_linear(a, int(col0), w, out, int(kind))
+        self.ext.head_linear(a, int(col0), w, out, int(kind), int(a_head_cols), int(out_head_cols))
         self.launches += 1
         return out
 
+    def latent_rope_write(self, proj, *, q_col0=0, q_weight=None, kv_col0=0, kv_weight=None, rot_dim=0,
+                          rot=0, eps, cos=None, sin=None, pages=None, positions, token_seq, block_tables,
+                          out_dtype):
+        """Of each row of ``proj``: the query latent (columns ``q_col0 ..``, as many as ``q_weight``
+        has values) RMS-normed and returned ``[T, query rank]``; the key/value latent (columns
+        ``kv_col0 ..``, as many as ``kv_weight`` has) RMS-normed and, behind it, the ``rot_dim``
+        columns of the shared key part with their first ``rot`` dims turned by the token's position
+        (neighbouring dims paired; ``cos``/``sin`` ``[positions, rot/2]``), written as one row of
+        the token's page. Either side may be absent (its weight None)."""
+        cq = None
+        if q_weight is not None:
+            cq = torch.empty(proj.shape[0], q_weight.numel(), dtype=out_dtype, device=proj.device)
+        self.ext.latent_rope_write(proj, int(q_col0), q_weight, cq, int(kv_col0), kv_weight, int(rot_dim), int(rot),
+                                   float(eps), cos, sin, pages if kv_weight is not None else None, positions,
+                                   token_seq, block_tables)
+        self.launches += 1
+        return cq
+
+    def latent_query_rope(self, q, out, *, num_heads, head_dim, rot_dim, rot, cos, sin, positions, rank):
+        """``q [T, H * (head_dim + rot_dim)]``: every head's last ``rot_dim`` dims, turned by the
+        position, go behind the ``rank`` dims of the head's slot in ``out [T, H * slot]``; what is
+        left of the slot is zeroed."""
+        self.ext.latent_query_rope(q, int(num_heads), int(head_dim), int(rot_dim), int(rot), cos, sin, positions,
+                                   out, int(rank))
+        self.launches += 1
+        return out
+
+    def sigmoid_gate_mul(self, o, g, col0, group):
+        """``o[t, i] *= sigmoid(g[t, col0 + i // group])`` in place; returns ``o``."""
+        self.ext.sigmoid_gate_mul(o, g, int(col0), int(group))
+        self.launches += 1
+        return o
+
+    _PLAIN_ACTIVATIONS = {"relu2": 0, "relu": 1, "gelu_tanh": 2, "silu": 3}
+
+    def activation(self, z, activation, out_dtype):
+        """``act(z)`` element by element in ``out_dtype``; relu2 is the square of relu."""
+        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+        self.ext.act_rows(z, out, self._PLAIN_ACTIVATIONS[activation])
+        self.launches += 1
+        return out
+
+    def activated_linear(self, h, w, activation, out_dtype):
+        """``act(h @ w.T)``. With few bfloat16 rows the activation meets the product as float32
+        values (it takes the product's fixed-point sums)."""
+        if self._few_rows(h, w) and out_dtype == torch.bfloat16:
+            sums = self._product_sums(h, w, None)
+            out = self.activation(sums, activation, out_dtype)
+            self._sums_taken(sums)
+            return out
+        return self.activation(self.linear(h, w, None, out_dtype=torch.float32), activation, out_dtype)
+
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, h, router, num_experts, top, has_gate):
-        """Sigmoid router scores in float32; returns (experts ``[T, top]`` int32, their scores
-        ``[T, top]``, the shared expert's gate ``[T]`` or None)."""
+    _ROUTER_WEIGHTS = {"sigmoid": 0, "softmax_of_chosen": 1}
+
+    def moe_route(self, h, router, num_experts, top, has_gate, bias=None, weights="sigmoid"):
+        """Router logits (+ ``bias``) in float32; returns (the ``top`` experts with the largest
+        logits ``[T, top]`` int32, their weights ``[T, top]``, the shared expert's gate ``[T]`` or
+        None). ``weights``: ``sigmoid`` of each chosen logit, or ``softmax_of_chosen``: the softmax
+        over the chosen logits alone."""
         T = h.shape[0]
         idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
         wts = torch.empty(T, top, dtype=torch.float32, device=h.device)
         gate = torch.empty(T, dtype=torch.float32, device=h.device) if has_gate else None
-        self.ext.moe_route(h, router, int(num_experts), int(top), idx, wts, gate)
+        self.ext.moe_route(h, router, int(num_experts), int(top), idx, wts, gate, bias, self._ROUTER_WEIGHTS[weights])
         self.launches += 1
         return idx, wts, gate
 
@@ -535,14 +597,15 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def moe_combine(self, y, plan, top, shared, gate, residual):
-        """Per token the sum of its experts' rows of ``y`` (+ gate * shared): added into
-        ``residual`` (returns None) or returned."""
+    def moe_combine(self, y, plan, top, shared, gate, residual, wts=None):
+        """Per token the sum of its experts' rows of ``y``, each times its weight if ``wts``
+        ``[T, top]`` is given, (+ gate * shared; no gate: + shared): added into ``residual``
+        (returns None) or returned."""
         work, num_experts = plan.work, plan.num_experts
         T = y.shape[0] // top
         out = residual if residual is not None else torch.empty(T, y.shape[1], dtype=torch.float32, device=y.device)
         self.ext.moe_combine(y, work, int(num_experts), int(top), shared, gate if shared is not None else None,
-                             out, residual is not None)
+                             out, residual is not None, wts)
         self.launches += 1
         return None if residual is not None else out
 

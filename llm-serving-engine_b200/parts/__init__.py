@@ -22,11 +22,11 @@ from .base import (
     StateNeed,
     role_dtype,
 )
-from .blocks import BranchNormBlock, BranchNormBlockSpec, PreNormBlock, PreNormBlockSpec
+from .blocks import BranchNormBlock, BranchNormBlockSpec, PreNormBlock, PreNormBlockSpec, SandwichBlock, SandwichBlockSpec
 from .linear_attention import DecayLinearAttention, DecayLinearAttentionSpec
 from .parallel import ParallelMixer, ParallelMixerSpec
 from .token_shift import TokenShift, TokenShiftSpec
-from .feed_forward import SwiGLU, SwiGLUSpec
+from .feed_forward import MLP, MLPSpec, SwiGLU, SwiGLUSpec
 from .norms import RMSNorm, RMSNormSpec
 from .embed_terms import HashedPairEmbedding, HashedPairSpec
 from .latent_attention import LatentAttention, LatentAttentionSpec
@@ -41,5 +41,5 @@ __all__ = [
     "RotaryPositionEncoding", "RotarySpec", "INPUT_FILTERS", "BranchNormBlock", "BranchNormBlockSpec",
     "DecayLinearAttention", "DecayLinearAttentionSpec", "ParallelMixer", "ParallelMixerSpec", "TokenShift",
     "TokenShiftSpec", "HashedPairEmbedding", "HashedPairSpec", "LatentAttention", "LatentAttentionSpec",
-    "RoutedExperts", "RoutedExpertsSpec", "SinusoidSpec",
+    "RoutedExperts", "RoutedExpertsSpec", "SinusoidSpec", "SandwichBlock", "SandwichBlockSpec", "MLP", "MLPSpec",
 ]

@@ -22,7 +22,16 @@ Further options of the spec, all off by default:
 * ``head_temperature``: a learned number per query head multiplies its scores;
 * ``distance_slopes``: ``slope_h * (i - j)`` is taken off the score of query i and key j;
 * ``chunk``: query i reads key j only if ``i // chunk == j // chunk`` (positions count from the
-  start of the sequence, however the prompt was cut).
+  start of the sequence, however the prompt was cut);
+* ``qk_norm_weight=False``: the q/k norm has no weight (a plain division by the root mean square);
+* ``value_dim``: values have another size than queries and keys; the kernels then run on heads
+  of the larger size, with zero rows and columns filling the smaller one up;
+* ``keep_first``: with a window, the sequence's first ``keep_first`` keys stay visible to every
+  later query beside its window, at their true positions; their pages are never given back;
+* ``gate``: the heads' outputs are multiplied by ``sigmoid(Wg h)`` before the output projection,
+  ``element`` by element (``Wg`` has as many rows as the concatenated heads) or ``head`` by head
+  (one row per head); ``Wg`` reads the same ``h`` and its rows follow v's in the fused matrix;
+* ``o_bias``: whether the output projection has a bias (None: as ``bias`` says).
 """
 
 from __future__ import annotations
@@ -50,6 +59,11 @@ class AttentionSpec:
     head_temperature: bool = False
     distance_slopes: tuple[float, ...] | None = None
     chunk: int = 0
+    qk_norm_weight: bool = True
+    value_dim: int | None = None  # None: head_dim
+    keep_first: int = 0
+    gate: str = "none"  # "element", "head"
+    o_bias: bool | None = None  # None: as bias
     kind: str = "attention"
 
 
@@ -59,20 +73,31 @@ class PagedAttention(Mixer):
         super().__init__(spec, env)
         if spec.num_heads % spec.num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if spec.gate not in ("none", "element", "head"):
+            raise ValueError(f"attention: gate {spec.gate!r} is not known")
+        if spec.keep_first and (spec.window <= 0 or spec.chunk > 0):
+            raise ValueError("attention: keep_first needs a window and no chunks")
+        self.value_dim = spec.head_dim if spec.value_dim is None else spec.value_dim
+        if spec.values_are_keys and self.value_dim != spec.head_dim:
+            raise ValueError("attention: values that are keys have the keys' size")
         self.q_size = spec.num_heads * spec.head_dim
         self.kv_size = spec.num_kv_heads * spec.head_dim
         self.position = POSITION_ENCODINGS.build(spec.position, env)
         self.rotary = self.position.rotary_tables()
-        self.v_size = 0 if spec.values_are_keys else self.kv_size
+        self.v_size = 0 if spec.values_are_keys else spec.num_kv_heads * self.value_dim
+        self.gate_size = {"none": 0, "element": spec.num_heads * self.value_dim, "head": spec.num_heads}[spec.gate]
+        self.o_bias_on = spec.bias if spec.o_bias is None else spec.o_bias
         # the plain path (fused projection, rotation, cache write and attention) serves none of these
         self.extended = (spec.qk_norm_eps is not None or spec.values_are_keys or spec.head_temperature
-                         or spec.distance_slopes is not None or spec.chunk > 0)
+                         or spec.distance_slopes is not None or spec.chunk > 0
+                         or self.value_dim != spec.head_dim or spec.keep_first > 0 or spec.gate != "none")
         # The attention kernels take head sizes that are multiples of 16. With the score options on,
         # any other head size is padded with zeros up to the next one when the weights are bound:
         # zero dims change no dot product, the norm divides by the true size, and the padded dims
         # of the output (values are zero there) meet zero columns of the output projection.
-        self.pad = (-spec.head_dim) % 16 if self.extended else 0
-        self.kernel_dim = spec.head_dim + self.pad
+        widest = max(spec.head_dim, self.value_dim)
+        self.kernel_dim = widest + ((-widest) % 16 if self.extended else 0)
+        self.pad = self.kernel_dim - spec.head_dim  # of a query or key head; a value head's may differ
         if self.pad and self.rotary is not None:
             raise NotImplementedError("a padded head size with rotary positions")
         self.slopes = None
@@ -85,13 +110,15 @@ class PagedAttention(Mixer):
     def param_decls(self):
         s = self.spec
         decls = {
-            "qkv.weight": ParamDecl((self.q_size + self.kv_size + self.v_size, s.hidden_size), "matrix"),
-            "o.weight": ParamDecl((s.hidden_size, self.q_size), "matrix"),
+            # rows: q, k, v heads, then the gate's
+            "qkv.weight": ParamDecl((self.q_size + self.kv_size + self.v_size + self.gate_size, s.hidden_size), "matrix"),
+            "o.weight": ParamDecl((s.hidden_size, s.num_heads * self.value_dim), "matrix"),
         }
         if s.bias:
             decls["qkv.bias"] = ParamDecl((self.q_size + self.kv_size + self.v_size,), "bias")
+        if self.o_bias_on:
             decls["o.bias"] = ParamDecl((s.hidden_size,), "bias")
-        if s.qk_norm_eps is not None:
+        if s.qk_norm_eps is not None and s.qk_norm_weight:
             decls["q_norm.weight"] = ParamDecl((s.head_dim,), "scale")
             decls["k_norm.weight"] = ParamDecl((s.head_dim,), "scale")
         if s.head_temperature:
@@ -106,29 +133,48 @@ class PagedAttention(Mixer):
         self.q_norm_weight = params.get("q_norm.weight")
         self.k_norm_weight = params.get("k_norm.weight")
         self.temperature = params.get("temperature")
-        if self.pad:
-            s, D, Dp = self.spec, self.spec.head_dim, self.kernel_dim
-            heads = self.qkv_weight.shape[0] // D
+        s = self.spec
+        if s.qk_norm_eps is not None and not s.qk_norm_weight:  # the kernel's norm multiplies by a weight: ones
+            self.q_norm_weight = self.k_norm_weight = torch.ones(s.head_dim, dtype=torch.float32, device=self.env.device)
+        if self.gate_size and self.qkv_bias is not None:  # the gate has no bias
+            self.qkv_bias = torch.cat([self.qkv_bias, self.qkv_bias.new_zeros(self.gate_size)])
+        if self.kernel_dim != s.head_dim or self.kernel_dim != self.value_dim:
+            self._pad_heads()
 
-            def pad_rows(w):  # [heads * D, ...] -> [heads * Dp, ...], zeros after each head's rows
-                out = w.new_zeros((heads, Dp) + tuple(w.shape[1:]))
-                out[:, :D] = w.view((heads, D) + tuple(w.shape[1:]))
-                return out.view((heads * Dp,) + tuple(w.shape[1:])).contiguous()
+    def _pad_heads(self):
+        """Every head's rows of q, k and v (and of a gate per element) filled up with zero rows to
+        the kernels' head size, the output projection with zero columns to match."""
+        s, D, V, Dp = self.spec, self.spec.head_dim, self.value_dim, self.kernel_dim
+        H, G = s.num_heads, s.num_kv_heads
+        parts = [(H, D), (G, D)] + ([] if s.values_are_keys else [(G, V)])
+        if s.gate == "element":
+            parts.append((H, V))
 
-            self.qkv_weight = pad_rows(self.qkv_weight)
-            if self.qkv_bias is not None:
-                self.qkv_bias = pad_rows(self.qkv_bias)
-            o = self.o_weight.new_zeros(s.hidden_size, s.num_heads, Dp)
-            o[:, :, :D] = self.o_weight.view(s.hidden_size, s.num_heads, D)
-            self.o_weight = o.view(s.hidden_size, s.num_heads * Dp).contiguous()
-            if self.q_norm_weight is not None:
-                self.q_norm_weight = torch.nn.functional.pad(self.q_norm_weight, (0, self.pad))
-                self.k_norm_weight = torch.nn.functional.pad(self.k_norm_weight, (0, self.pad))
+        def pad_rows(w):  # rows of the fused matrix (or entries of its bias), head by head
+            out, at = [], 0
+            for heads, d in parts:
+                piece = w[at : at + heads * d]
+                at += heads * d
+                padded = w.new_zeros((heads, Dp) + tuple(w.shape[1:]))
+                padded[:, :d] = piece.view((heads, d) + tuple(w.shape[1:]))
+                out.append(padded.view((heads * Dp,) + tuple(w.shape[1:])))
+            out.append(w[at:])  # a gate per head: one row each, as it is
+            return torch.cat(out, 0).contiguous()
+
+        self.qkv_weight = pad_rows(self.qkv_weight)
+        if self.qkv_bias is not None:
+            self.qkv_bias = pad_rows(self.qkv_bias)
+        o = self.o_weight.new_zeros(s.hidden_size, H, Dp)
+        o[:, :, :V] = self.o_weight.view(s.hidden_size, H, V)
+        self.o_weight = o.view(s.hidden_size, H * Dp).contiguous()
+        if self.q_norm_weight is not None:
+            self.q_norm_weight = torch.nn.functional.pad(self.q_norm_weight, (0, Dp - D))
+            self.k_norm_weight = torch.nn.functional.pad(self.k_norm_weight, (0, Dp - D))
 
     # what the cache manager has to keep for a layer of this kind
     def cache_need(self):
         s = self.spec
-        return PagedKVNeed(s.num_kv_heads, self.kernel_dim, s.window)
+        return PagedKVNeed(s.num_kv_heads, self.kernel_dim, s.window, keep_first=s.keep_first)
 
     def reserve(self, max_seqs: int) -> None:
         """Allocate kernel scratch for up to ``max_seqs`` single-token sequences in a step."""
@@ -185,7 +231,7 @@ class PagedAttention(Mixer):
 
     def _extended(self, h, step, cache, tables, cos, sin):
         """Projection (its sums unrounded), norm / rotation / cache write, attention with the
-        score options: three launches."""
+        score options: three launches, and one more with an output gate."""
         s, ops = self.spec, self.ops
         qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=torch.float32)
         q = ops.norm_rope_kv_write(
@@ -196,8 +242,12 @@ class PagedAttention(Mixer):
             positions=step.positions, token_seq=step.token_seq, cos=cos, sin=sin,
             k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,
             block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)
-        return ops.paged_attention(
+        o = ops.paged_attention(
             q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim, scale=s.scale,
             window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
             page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
-            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk)
+            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk, keep_first=s.keep_first)
+        if s.gate != "none":  # the gate's columns follow v's in the projection's rows
+            col0 = (s.num_heads + s.num_kv_heads * (1 if s.values_are_keys else 2)) * self.kernel_dim
+            ops.sigmoid_gate_mul(o, qkv, col0, 1 if s.gate == "element" else self.kernel_dim)
+        return o

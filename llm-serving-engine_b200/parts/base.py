@@ -83,6 +83,8 @@ class PagedKVNeed:
 
     window: 0 keeps every token; ``w > 0`` means a query at position p reads keys p-w+1 .. p only,
     so pages that lie wholly before that range can be given back while the request is still live.
+    keep_first: with a window, the request's first ``keep_first`` tokens stay readable for good,
+    so the pages that hold any of them are never given back before the request ends.
     """
 
     num_kv_heads: int
@@ -91,6 +93,7 @@ class PagedKVNeed:
     kind: str = "paged_kv"
     dtype: object = None  # of the pages; None: the model's compute dtype (what the attention kernels here read)
     values: bool = True  # False: one row per token only (a latent row that serves as key and value alike)
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -161,6 +164,12 @@ class Norm(Part):
 
     def add_normed(self, x, branch, emit=True):  # pragma: no cover - interface
         raise NotImplementedError
+
+    def add_normed_then(self, x, branch, then: "Norm"):
+        """``x += norm(branch)`` followed by ``then.forward(x)``: the rows that the next sublayer
+        reads. A norm whose kernels can do both while they hold the row overrides this."""
+        self.add_normed(x, branch, emit=False)
+        return then.forward(x)
 
 
 @dataclass

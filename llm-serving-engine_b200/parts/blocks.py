@@ -12,6 +12,12 @@ that reads ``x`` next, so a block returns its feed-forward output as ``pending``
 
     x <- x + norm_mixer(mixer(filter(x)));   x <- x + norm_ff(feed_forward(x))
 
+``sandwich``: a norm before and a norm after each sublayer:
+
+    x <- x + norm_mixer_out(mixer(norm_in(x)));   x <- x + norm_ff_out(feed_forward(norm_post(x)))
+
+(the second half is optional).
+
 ``filter`` is an optional input filter of the mixer (a token shift, say); the feed-forward is
 optional too. A filter that keeps something per request shares the block's cache layer with the
 mixer: the mixer's needs come first, the filter's states after them.
@@ -120,4 +126,51 @@ class BranchNormBlock(Block):
             else:
                 f = self.feed_forward.forward(h, step)
             self.norm_ff.add_normed(x, f, emit=False)
+        return x, None
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    norm_in: Any
+    mixer: Any
+    norm_mixer_out: Any
+    norm_post: Any = None  # None together with feed_forward and norm_ff_out: the layer is its mixer alone
+    feed_forward: Any = None
+    norm_ff_out: Any = None
+    kind: str = "sandwich"
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    def __init__(self, spec: SandwichBlockSpec, env) -> None:
+        super().__init__(spec, env)
+        self.children = {
+            "norm_in": NORMS.build(spec.norm_in, env),
+            "mixer": MIXERS.build(spec.mixer, env),
+            "norm_mixer_out": NORMS.build(spec.norm_mixer_out, env),
+        }
+        if spec.feed_forward is not None:
+            self.children["norm_post"] = NORMS.build(spec.norm_post, env)
+            self.children["feed_forward"] = FEED_FORWARDS.build(spec.feed_forward, env)
+            self.children["norm_ff_out"] = NORMS.build(spec.norm_ff_out, env)
+        for name, child in self.children.items():
+            setattr(self, name, child)
+        self.feed_forward = self.children.get("feed_forward")
+
+    def forward(self, x, pending, step, cache):
+        h = self.norm_in.forward(x, settle(pending, self.norm_in))
+        if getattr(self.mixer, "accepts_deferral", False):
+            a = self.mixer.forward(h, step, cache, may_defer=True)  # may be a product still lying as sums
+        else:
+            a = self.mixer.forward(h, step, cache)
+        if self.feed_forward is None:
+            self.norm_mixer_out.add_normed(x, a, emit=False)
+            return x, None
+        # x += norm(a), and the next norm of the new x, in the norm's own way (one launch if it can)
+        h = self.norm_mixer_out.add_normed_then(x, a, self.norm_post)
+        if getattr(self.feed_forward, "accepts_residual", False):
+            f = self.feed_forward.forward(h, step, may_defer=True)
+        else:
+            f = self.feed_forward.forward(h, step)
+        self.norm_ff_out.add_normed(x, f, emit=False)
         return x, None

@@ -5,6 +5,9 @@
                                          gelu_tanh: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
 
 No biases. The activation is computed in float32 (src/llmserve/kernels/csrc/fused_ops.cpp:75-91).
+
+``mlp`` is the ungated form, ``y = Wdown act(Wup h)``, with ``act`` one of ``relu2`` (the square of
+relu), ``relu``, ``gelu_tanh``, ``silu``.
 """
 
 from __future__ import annotations
@@ -50,3 +53,39 @@ class SwiGLU(FeedForward):
             a = ops.gated_silu(h, self.gate_up_weight, None, out_dtype=self.env.dtype,
                                activation=self.spec.activation)
         return project_into(ops, a, self.down_weight, None, self.env.residual_dtype, residual, may_defer)
+
+
+PLAIN_ACTIVATIONS = ("relu2", "relu", "gelu_tanh", "silu")
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "mlp"
+
+
+@FEED_FORWARDS.register("mlp")
+class MLP(FeedForward):
+    accepts_residual = True
+
+    def __init__(self, spec: MLPSpec, env) -> None:
+        super().__init__(spec, env)
+        if spec.activation not in PLAIN_ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation {spec.activation!r} is not known")
+
+    def param_decls(self):
+        s = self.spec
+        return {
+            "up.weight": ParamDecl((s.intermediate_size, s.hidden_size), "matrix"),
+            "down.weight": ParamDecl((s.hidden_size, s.intermediate_size), "matrix"),
+        }
+
+    def bind(self, params):
+        self.up_weight = params["up.weight"]
+        self.down_weight = params["down.weight"]
+
+    def forward(self, h, step, residual=None, may_defer=False):
+        a = self.ops.activated_linear(h, self.up_weight, self.spec.activation, self.env.dtype)
+        return project_into(self.ops, a, self.down_weight, None, self.env.residual_dtype, residual, may_defer)

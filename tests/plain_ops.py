@@ -137,7 +137,7 @@ class PlainOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan=None, head_scale=None,
-                        slopes=None, chunk=0, sinks=None):
+                        slopes=None, chunk=0, sinks=None, keep_first=0):
         T, D = q.shape[0], head_dim
         qkv = q
         q = q[:, : num_heads * D].float().reshape(T, num_heads, D)
@@ -155,7 +155,7 @@ class PlainOps:
             qpos = torch.arange(ctx[s] - n, ctx[s])[:, None]
             visible = j[None, :] <= qpos
             if window > 0:
-                visible &= (qpos - j[None, :]) < window
+                visible &= ((qpos - j[None, :]) < window) | (j[None, :] < keep_first)
             if chunk > 0:
                 visible &= (qpos // chunk) == (j[None, :] // chunk)
             sc = torch.einsum("thd,shd->hts", q[a:b], k) * scale
@@ -176,7 +176,7 @@ class PlainOps:
         T, D = qkv.shape[0], head_dim
         nd = norm_dim or head_dim
         nv = 0 if values_are_keys else num_kv_heads
-        heads = qkv.float().view(T, num_heads + num_kv_heads + nv, D)
+        heads = qkv[:, : (num_heads + num_kv_heads + nv) * D].float().reshape(T, num_heads + num_kv_heads + nv, D)
         q, k = heads[:, :num_heads], heads[:, num_heads : num_heads + num_kv_heads]
         v = k if values_are_keys else heads[:, num_heads + num_kv_heads :]
         if q_weight is not None:
@@ -222,29 +222,99 @@ class PlainOps:
         pages[page, 0, pos % page_tokens] = 0
         pages[page, 0, pos % page_tokens, :rank] = c.to(pages.dtype)
 
-    def head_linear(self, a, col0, w, out_dtype):
+    def head_linear(self, a, col0, w, out_dtype, a_head_cols=0, out_head_cols=0):
         H, N, K = w.shape
-        x = a[:, col0 : col0 + H * K].float().view(-1, H, K)
-        return torch.einsum("thk,hnk->thn", x, w.float()).reshape(-1, H * N).to(out_dtype)
+        ah, oh = a_head_cols or K, out_head_cols or N
+        x = a[:, col0 : col0 + H * ah].float().reshape(-1, H, ah)[:, :, :K]
+        out = torch.zeros(a.shape[0], H, oh)
+        out[:, :, :N] = torch.einsum("thk,hnk->thn", x, w.float())
+        return out.reshape(-1, H * oh).to(out_dtype)
+
+    @staticmethod
+    def _turn_neighbours(x, rot, cos, sin, pos):
+        """x [T, ..., d]: the pairs (2i, 2i+1) of the first ``rot`` dims turned by the position's angles."""
+        if not rot:
+            return x
+        shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (rot // 2,)
+        c, s_ = cos[pos].reshape(shape), sin[pos].reshape(shape)
+        out = x.clone()
+        u, v = x[..., 0:rot:2], x[..., 1:rot:2]
+        out[..., 0:rot:2] = u * c - v * s_
+        out[..., 1:rot:2] = v * c + u * s_
+        return out
+
+    def latent_rope_write(self, proj, *, q_col0=0, q_weight=None, kv_col0=0, kv_weight=None, rot_dim=0,
+                          rot=0, eps, cos=None, sin=None, pages=None, positions, token_seq, block_tables,
+                          out_dtype):
+        pos = positions.long()
+        cq = None
+        if q_weight is not None:
+            d = proj[:, q_col0 : q_col0 + q_weight.numel()].float()
+            cq = (d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * q_weight).to(out_dtype)
+        if kv_weight is not None:
+            R = kv_weight.numel()
+            d = proj[:, kv_col0 : kv_col0 + R].float()
+            c = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * kv_weight
+            kr = self._turn_neighbours(proj[:, kv_col0 + R : kv_col0 + R + rot_dim].float(), rot, cos, sin, pos)
+            page_tokens = pages.shape[2]
+            page = block_tables[token_seq.long(), pos // page_tokens].long()
+            pages[page, 0, pos % page_tokens] = 0
+            pages[page, 0, pos % page_tokens, : R + rot_dim] = torch.cat([c, kr], -1).to(pages.dtype)
+        return cq
+
+    def latent_query_rope(self, q, out, *, num_heads, head_dim, rot_dim, rot, cos, sin, positions, rank):
+        T = q.shape[0]
+        qr = q.float().reshape(T, num_heads, head_dim + rot_dim)[:, :, head_dim:]
+        qr = self._turn_neighbours(qr, rot, cos, sin, positions.long())
+        slots = out.view(T, num_heads, -1)
+        slots[:, :, rank:] = 0
+        slots[:, :, rank : rank + rot_dim] = qr.to(out.dtype)
+        return out
+
+    def sigmoid_gate_mul(self, o, g, col0, group):
+        cols = col0 + torch.arange(o.shape[1]) // group
+        o.copy_((o.float() * torch.sigmoid(g.float()[:, cols])).to(o.dtype))
+        return o
+
+    def activation(self, z, activation, out_dtype):
+        z = z.float()
+        if activation == "relu2":
+            y = torch.relu(z) ** 2
+        elif activation == "relu":
+            y = torch.relu(z)
+        elif activation == "gelu_tanh":
+            y = torch.nn.functional.gelu(z, approximate="tanh")
+        else:
+            y = torch.nn.functional.silu(z)
+        return y.to(out_dtype)
+
+    def activated_linear(self, h, w, activation, out_dtype):
+        return self.activation(self.linear(h, w, None, out_dtype=torch.float32), activation, out_dtype)
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, h, router, num_experts, top, has_gate):
-        z = torch.sigmoid(h.float() @ router.float().T)
-        val, idx = torch.topk(z[:, :num_experts], top, dim=-1)
-        return idx.to(torch.int32), val, (z[:, num_experts] if has_gate else None)
+    def moe_route(self, h, router, num_experts, top, has_gate, bias=None, weights="sigmoid"):
+        z = h.float() @ router.float().T
+        gate = torch.sigmoid(z[:, num_experts]) if has_gate else None
+        z = z[:, :num_experts] + (bias.float() if bias is not None else 0.0)
+        val, idx = torch.topk(z, top, dim=-1)
+        val = torch.sigmoid(val) if weights == "sigmoid" else torch.softmax(val, dim=-1)
+        return idx.to(torch.int32), val, gate
 
     def moe_sort(self, idx, num_experts, dtype, width=0, kind=None):
         return idx  # the plain products below walk the choices as they are
 
     def expert_linear(self, a, w, plan, top=0, wts=None):
         idx = plan.reshape(-1).long()
-        rows = a.float() if top == 0 else a.float().repeat_interleave(top, 0) * wts.reshape(-1, 1)
+        rows = a.float() if top == 0 else a.float().repeat_interleave(top, 0)
+        if wts is not None:
+            rows = rows * wts.reshape(-1, 1)
         return torch.einsum("rk,rnk->rn", rows, w.float()[idx])
 
-    def moe_combine(self, y, plan, top, shared, gate, residual):
-        out = y.view(-1, top, y.shape[1]).sum(1)
+    def moe_combine(self, y, plan, top, shared, gate, residual, wts=None):
+        rows = y.view(-1, top, y.shape[1])
+        out = (rows * wts[:, :, None]).sum(1) if wts is not None else rows.sum(1)
         if shared is not None:
-            out = out + gate[:, None] * shared.float()
+            out = out + (gate[:, None] * shared.float() if gate is not None else shared.float())
         if residual is not None and self.accumulate:
             residual += out
             return None
