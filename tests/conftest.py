@@ -273,3 +273,112 @@ def write_pazivik(folder, name):
 @pytest.fixture(scope="session")
 def pazivik_dirs(tmp_path_factory):
     return {name: write_pazivik(tmp_path_factory.mktemp(f"pazivik-{name}"), name) for name in PAZIVIK_TINY}
+
+
+# ---- Rirovik: small configurations that differ in every size, in the kinds and order of layers
+# and in which optional thing is there.
+def _rlat(kind, heads, dim, rot_dim, vdim, rank, q_rank, scale, base, mlp, window=0, kv_from=None, rot_dims=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "q_rank": q_rank,
+         "scale": scale, "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims}}
+    if window:
+        m["mask"] = {"size": window}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return {"type": kind, "mixer": m, "mlp": mlp}
+
+
+def _ratt(heads, kv, dim, vdim, scale, window, keep, mlp):
+    mask = {"size": window}
+    if keep:
+        mask["keep_first"] = keep
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale,
+                                           "mask": mask}, "mlp": mlp}
+
+
+RIROVIK_TINY = {
+    # values wider and narrower than keys; a reader whose window is wider than its writer's; a
+    # layer without feed-forward; experts without a shared one; every expert chosen; one expert
+    "R1": dict(seed=3, page_tokens=16, config={
+        "architecture": "Rirovik", "vocab": 211, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.5},
+        "layers": [_rlat("latent_attention_2", 3, 16, 8, 24, 40, 24, 0.3, 10000.0, _moe(5, 2, 24, 40)),
+                   _rlat("latent_attention", 2, 32, 16, 8, 32, 48, 0.2, 500.0, _moe(3, 1, 32, 0), window=20),
+                   _ratt(4, 2, 16, 32, 0.4, 12, 3, None),
+                   _rlat("latent_attention", 4, 8, 16, 16, 32, 16, 0.35, 500.0, _moe(4, 4, 16, 8), window=33, kv_from=1)]}),
+    # widths that are multiples of nothing; a window shorter than a page and one of a single
+    # token; more kept first tokens than the window holds; no kept tokens; one key/value head per
+    # query head; a rotated part of which only some dims turn; a cache row that needs padding
+    "R2": dict(seed=12, page_tokens=8, config={
+        "architecture": "Rirovik", "vocab": 130, "width": 70, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+        "layers": [_ratt(3, 3, 24, 10, 0.25, 5, 9, _moe(4, 2, 10, 16)),
+                   _rlat("latent_attention_2", 5, 8, 4, 12, 22, 10, 0.4, 100.0, _moe(2, 1, 30, 6), rot_dims=2),
+                   _rlat("latent_attention", 1, 20, 6, 6, 18, 14, 0.3, 30.0, None, window=1),
+                   _ratt(2, 1, 12, 12, 0.3, 40, 0, _moe(3, 3, 8, 0)),
+                   _rlat("latent_attention", 2, 12, 4, 20, 22, 9, 0.3, 100.0, _moe(4, 2, 12, 12), window=7, kv_from=1,
+                         rot_dims=2)]}),
+    # the head and latent sizes of larger models (a cache row beyond 128 dims); many experts;
+    # windows of exactly one page and of several; four query heads per key/value head
+    "R3": dict(seed=19, page_tokens=32, sharp=5, config={
+        "architecture": "Rirovik", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 11.3},
+        "layers": [_rlat("latent_attention", 8, 64, 32, 64, 128, 96, 0.1, 20000.0, _moe(16, 3, 48, 64), window=32),
+                   _ratt(8, 2, 64, 64, 0.125, 100, 4, _moe(2, 1, 64, 8)),
+                   _rlat("latent_attention_2", 4, 32, 16, 48, 48, 64, 0.15, 1000000.0, _moe(6, 2, 40, 0))]}),
+}
+
+
+def write_rirovik(folder, name):
+    """A random Rirovik folder whose weights are drawn wide: attention is far from flat, norms,
+    biases and gates differ clearly from dim to dim and head to head, so that leaving one of them
+    out, or reading a key too many, changes the logits clearly.
+
+    No routing decision is a close call (a model computed in bfloat16 must pick the same experts
+    as the float64 one): the last dims of the residual stream carry, for every token, one of
+    evenly spaced levels per expert, in an order that depends on the token; no layer writes
+    those dims (the norms behind the sublayers multiply them by 1 + (-1)), and each router row
+    reads its expert's dim with weight one beside small random weights on all the others."""
+    from safetensors.torch import load_file, save_file
+
+    from llmserve_b200.config.rirovik import RirovikConfig
+    from llmserve_b200.weights import write_random_model
+
+    spec = RIROVIK_TINY[name]
+    write_random_model(folder, RirovikConfig.from_dict(spec["config"]), spec["seed"])
+    f = folder / "model.safetensors"
+    t = load_file(str(f))
+    g = torch.Generator().manual_seed(spec["seed"] + 1)
+    for k, v in t.items():
+        if k.endswith("dq.norm") or k.endswith("dkv.norm"):
+            t[k] = (1.0 + (torch.rand(v.shape, generator=g) - 0.5)).to(v.dtype)
+        elif v.dim() == 1:  # norms stored around zero, biases
+            t[k] = (torch.rand(v.shape, generator=g) - 0.5).to(v.dtype)
+        elif k == "embed":
+            t[k] = (v.float() * 40 / spec["config"]["embedding"]["scale"]).to(v.dtype)
+        elif k.endswith(("mix.uq", "mix.uk", "mix.q", "mix.k")):
+            t[k] = (v.float() * spec.get("sharp", 10)).to(v.dtype)  # wider heads need less to be sharp
+        else:
+            t[k] = (v.float() * 8).to(v.dtype)
+    cfg = spec["config"]
+    width = cfg["width"]
+    moe = [(i, l["mlp"]["router"]["experts"]) for i, l in enumerate(cfg["layers"]) if l["mlp"] is not None]
+    most = max(e for _, e in moe)
+    step = next(m for m in (3, 5, 7, 11) if all(most % q or m % q for q in (2, 3, 5, 7, 11)))
+    dims = [width - most + e for e in range(most)]
+    tok = torch.arange(cfg["vocab"])[:, None]
+    levels = 1.5 * (((tok * 7 + step * torch.arange(most)[None, :]) % most).float() - (most - 1) / 2)
+    t["embed"][:, dims] = (levels / cfg["embedding"]["scale"]).to(t["embed"].dtype)
+    for i, l in enumerate(cfg["layers"]):
+        t[f"l{i}.norm1b"][dims] = -1
+        if l["mlp"] is not None:
+            t[f"l{i}.norm2b"][dims] = -1
+    for i, experts in moe:
+        t[f"l{i}.norm2"][dims] = 0
+        router = torch.randn(experts, width, generator=g) * 0.002
+        router[torch.arange(experts), dims[:experts]] = 1.0
+        t[f"l{i}.mlp.router"] = router.to(torch.bfloat16)
+        t[f"l{i}.mlp.router.b"] = (0.2 * (torch.rand(experts, generator=g) - 0.5)).to(torch.bfloat16)
+    save_file(t, str(f))
+    return folder
+
+
+@pytest.fixture(scope="session")
+def rirovik_dirs(tmp_path_factory):
+    return {name: write_rirovik(tmp_path_factory.mktemp(f"rirovik-{name}"), name) for name in RIROVIK_TINY}
