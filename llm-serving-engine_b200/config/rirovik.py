@@ -7,11 +7,11 @@ feed-forward under ``mlp`` (null: none). The mixers:
 
 * ``latent_attention`` and ``latent_attention_2``: ``heads``, ``dim``, ``rot_dim``, ``vdim``,
   ``kv_rank``, ``q_rank``, ``scale``, ``rot`` (``base``, ``dims``); ``latent_attention`` also has
-  ``mask.size`` (its window), an output gate per head, and may have ``kv_from``: the earlier layer
-  whose cached rows it reads instead of making its own. ``latent_attention_2`` sees every earlier
-  token and has no gate;
+  ``mask.size`` (its window) and an output gate per head; ``latent_attention_2`` sees every
+  earlier token and has no gate. Either may have ``kv_from``: the earlier layer whose cached rows
+  it reads instead of making its own;
 * ``attention``: ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``mask`` (``size`` and,
-  optionally, ``keep_first``).
+  optionally, ``keep_first``; without ``mask`` every earlier token is seen).
 
 The feed-forward is ``{"kind": "moe", "router": {"experts", "top"}, "expert": {"ff"}, "shared":
 {"ff"}}`` (``shared`` may be absent or null). Layers may differ in kind and in every size. A key
@@ -58,9 +58,9 @@ class RirovikLatentConfig:
     @classmethod
     def from_dict(cls, d, where, windowed: bool):
         required = ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale", "rot")
-        optional = ("mask", "kv_from") if windowed else ()
-        heads, dim, rot_dim, vdim, rank, q_rank, scale, rot, *rest = _take_some(d, required, optional, where)
-        mask, kv_from = rest if windowed else (None, None)
+        optional = ("kv_from", "mask") if windowed else ("kv_from",)
+        heads, dim, rot_dim, vdim, rank, q_rank, scale, rot, kv_from, *rest = _take_some(d, required, optional, where)
+        mask = rest[0] if windowed else None
         base, dims = _take(rot, ("base", "dims"), where + ".rot")
         window = _mask(mask, where)[0] if mask is not None else 0
         if windowed and not window:
@@ -95,18 +95,19 @@ class RirovikAttentionConfig:
 
     @classmethod
     def from_dict(cls, d, where):
-        heads, kv, dim, vdim, scale, mask = _take(d, ("heads", "kv_heads", "dim", "vdim", "scale", "mask"), where)
-        window, keep = _mask(mask, where, ("keep_first",))
+        heads, kv, dim, vdim, scale, mask = _take_some(d, ("heads", "kv_heads", "dim", "vdim", "scale"), ("mask",), where)
+        window, keep = _mask(mask, where, ("keep_first",)) if mask is not None else (0, 0)
         if min(int(heads), int(kv), int(dim), int(vdim)) < 1 or int(heads) % int(kv):
             raise ConfigError(f"{where}: sizes must be positive and heads a multiple of kv_heads")
         return cls(int(heads), int(kv), int(dim), int(vdim), float(scale), window, keep)
 
     def to_dict(self):
-        mask = {"size": self.window}
-        if self.keep_first:
-            mask["keep_first"] = self.keep_first
-        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
-                "scale": self.scale, "mask": mask}
+        d = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.window:
+            d["mask"] = {"size": self.window}
+            if self.keep_first:
+                d["mask"]["keep_first"] = self.keep_first
+        return d
 
 
 @dataclass(frozen=True)

@@ -64,7 +64,7 @@ def rirovik_plan(cfg: RirovikConfig) -> ModelPlan:
             mixer = AttentionSpec(
                 hidden_size=w, num_heads=m.heads, num_kv_heads=m.kv_heads, head_dim=m.dim, scale=m.scale,
                 position=NoPositionSpec(), bias=True, o_bias=False, window=m.window, qk_norm_eps=eps,
-                qk_norm_weight=False, value_dim=m.vdim, keep_first=m.keep_first, gate="element")
+                qk_norm_weight=False, value_dim=m.vdim, keep_first=m.keep_first if m.window else 0, gate="element")
         ff = None
         if l.mlp is not None:
             ff = RoutedExpertsSpec(w, l.mlp.experts, l.mlp.top, l.mlp.ff, l.mlp.shared_ff, activation="relu2",
