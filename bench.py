@@ -19,8 +19,10 @@ and a float32 replay of one 8192-token sequence against the plain implementation
 reference's own harness (src/llmserve/bench/run.py:96,124-176): fixed output lengths, greedy, a
 warm-up run that is thrown away, one JSON line with the environment.
 
-``--workload designs`` (``--arms llama,gubotar,pazivik``) puts four Pazivik layers (latent attention
-with a window; dense and routed feed-forwards) and four Gubotar layers (parallel, retention, retention, parallel) beside
+``--workload designs`` (``--arms llama,gubotar,pazivik,rirovik``) puts four Pazivik layers (latent attention
+with a window; dense and routed feed-forwards), four Gubotar layers (parallel, retention, retention, parallel) and
+four Rirovik layers (latent attention with a query latent and a rotated key part, without and with a window;
+attention that keeps the first keys; routed ungated experts everywhere) beside
 four Llama layers of the same width, feed-forward and head sizes, at SmolLM2-360M and -1.7B layer
 sizes: a 2048-token prompt in one step, with its device time by kernel, and decode steps at batch
 1, 8 and 64 behind 2048-token prompts.
@@ -605,6 +607,33 @@ def pazivik_layers(width, heads, head_dim, ff, rank=128, window=1024, experts=8,
     return [layer(dense), layer(moe, 0), layer(dense), layer(moe, 2)]
 
 
+def rirovik_layers(width, heads, kv_heads, head_dim, ff, rank=96, rot_dim=32, window=1024, keep_first=4,
+                   experts=8, top=2):
+    """Four Rirovik layers at a Llama layer's sizes. Three have the Llama layer's heads on a latent of
+    ``rank`` dims beside ``rot_dim`` rotated ones (a cached row of ``rank + rot_dim`` dims: with the
+    defaults as wide as the Pazivik arm's), queries from a latent of a quarter of the width: one
+    that sees everything, one with a window, and one with a window that reads the second's rows.
+    One has the Llama layer's grouped heads without positions, a window and kept first keys.
+    Every feed-forward is ``experts`` ungated experts of a quarter of the Llama layer's size,
+    ``top`` per token, beside a shared one."""
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // 4},
+           "shared": {"ff": ff // 4}}
+
+    def latent(kind, kv_from=None):
+        m = {"heads": heads, "dim": head_dim, "rot_dim": rot_dim, "vdim": head_dim, "kv_rank": rank,
+             "q_rank": width // 4, "scale": (head_dim + rot_dim) ** -0.5, "rot": {"base": 10000.0, "dims": rot_dim}}
+        if kind == "latent_attention":
+            m["mask"] = {"size": window}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": kind, "mixer": m, "mlp": moe}
+
+    plain = {"type": "attention", "mlp": moe, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+        "mask": {"size": window, "keep_first": keep_first}}}
+    return [latent("latent_attention_2"), latent("latent_attention"), plain, latent("latent_attention", 1)]
+
+
 def kernel_profile(fn, reps=3) -> dict:
     """Device time of ``fn()`` by kernel, from the framework's profiler: microseconds per call."""
     import collections
@@ -646,6 +675,8 @@ def designs_main(args) -> int:
                                                  "layers": gubotar_layers(w, heads, kv, hd, ff, state_dim=hd if w < 2048 else 128)}),
             "pazivik": ("random:pazivik-2048", {"width": w, "vocab": ll["vocab_size"],
                                                  "layers": pazivik_layers(w, heads, hd, ff)}),
+            "rirovik": ("random:rirovik-2048", {"width": w, "vocab": ll["vocab_size"],
+                                                 "layers": rirovik_layers(w, heads, kv, hd, ff)}),
         }
         arms = {k: v for k, v in arms.items() if k in args.arms.split(",")}
         row = {"sizes": f"{alias}: width {w}, ff {ff}, {heads} heads of {hd}, 4 layers"}
@@ -797,7 +828,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "continuous", "long", "designs"])
-    ap.add_argument("--arms", default="llama,gubotar,pazivik",
+    ap.add_argument("--arms", default="llama,gubotar,pazivik,rirovik",
                     help="--workload designs: which architectures run side by side")
     ap.add_argument("--model", default="smollm2-1.7b")
     ap.add_argument("--batch", type=int, default=8)
