@@ -646,7 +646,8 @@ const float* opt_f32(const OptTensor& t, int64_t n, const char* what) {
 }
 
 void rmsnorm_add(Tensor& x, const Tensor& a, const OptTensor& b, const OptTensor& wa, const OptTensor& wb,
-                 double ca, double cb, double eps_in, const Tensor& w, double eps, const OptTensor& out) {
+                 double ca, double cb, double eps_in, const Tensor& w, double eps, const OptTensor& out,
+                 const OptTensor& then_w, double then_eps) {
   check_f32(x, "x");
   check_cuda(a, "a");
   check_f32(w, "w");
@@ -670,9 +671,10 @@ void rmsnorm_add(Tensor& x, const Tensor& a, const OptTensor& b, const OptTensor
     op = out->data_ptr();
     oc = out_code(*out, "out");
   }
+  TORCH_CHECK(!then_w || out, "rmsnorm_add: the norm that follows needs an output tensor");
   done(lse_rmsnorm_add(x.data_ptr<float>(), a.data_ptr(), bp, branch_code, opt_f32(wa, H, "wa"), opt_f32(wb, H, "wb"),
                        (float)ca, (float)cb, (float)eps_in, w.data_ptr<float>(), (float)eps, op, oc,
-                       (int)x.size(0), (int)H, stream()),
+                       opt_f32(then_w, H, "then_w"), (float)then_eps, (int)x.size(0), (int)H, stream()),
        "rmsnorm_add");
 }
 

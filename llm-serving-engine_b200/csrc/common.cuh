@@ -60,6 +60,46 @@ __device__ __forceinline__ void store16(T* p, const Vec16<T>& r) {
   *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
 }
 
+// Four consecutive elements as floats (the address a multiple of four elements' size).
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+// Fixed-point sums are taken: read, converted, and zeros left behind for the next sums.
+template <>
+__device__ __forceinline__ void load4<fixed64>(const fixed64* p, float (&v)[4]) {
+  longlong2* q = reinterpret_cast<longlong2*>(const_cast<fixed64*>(p));
+  const longlong2 a = q[0], b = q[1];
+  q[0] = make_longlong2(0, 0);
+  q[1] = make_longlong2(0, 0);
+  v[0] = fixed_to_float(a.x); v[1] = fixed_to_float(a.y);
+  v[2] = fixed_to_float(b.x); v[3] = fixed_to_float(b.y);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

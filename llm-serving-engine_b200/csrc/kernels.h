@@ -125,10 +125,12 @@ int lse_token_shift(const float* x, const float* mix, float* state, void* out, i
 // y = a, or with wa: ca * wa * a / rms(a) (+ cb * wb * b / rms(b) if b); x += w * y / rms(y);
 // out (may be null) = the new x in out_dtype. rms(v) = sqrt(mean(v^2) + eps), eps_in for a and b.
 // branch_dtype: LSE_F32, or LSE_FIXED64 when a (and b) are the sums of few-rows products, which are
-// taken (left zero); then H * (b ? 2 : 1) floats must fit 48 KB of shared memory.
+// taken (left zero); then H * (b ? 2 : 1) floats must fit 48 KB of shared memory. With then_w,
+// out = then_w * x / rms(x) of the new x (eps then_eps) instead of the new x itself.
 int lse_rmsnorm_add(float* x, const void* a, const void* b, int branch_dtype, const float* wa,
                     const float* wb, float ca, float cb, float eps_in, const float* w, float eps,
-                    void* out, int out_dtype, int T, int H, cudaStream_t stream);
+                    void* out, int out_dtype, const float* then_w, float then_eps, int T, int H,
+                    cudaStream_t stream);
 // out = ca * wa * a / rms(a) (+ cb * wb * b / rms(b) if b)
 int lse_mix_normed(const float* a, const float* b, const float* wa, const float* wb, float ca,
                    float cb, float eps, float* out, int T, int H, cudaStream_t stream);

@@ -38,45 +38,6 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 // ------------------------------------------------------------------------------------ rms norm
 // One block per output row. The row is visited twice by the same threads at the same indices, so
 // the second visit sees this thread's own writes of the first.
-template <typename T>
-__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
-template <>
-__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
-  const float4 t = *reinterpret_cast<const float4*>(p);
-  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-}
-template <>
-__device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
-  const uint2 t = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
-  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
-  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
-}
-// Fixed-point sums are taken: read, converted, and zeros left behind for the next sums.
-template <>
-__device__ __forceinline__ void load4<fixed64>(const fixed64* p, float (&v)[4]) {
-  longlong2* q = reinterpret_cast<longlong2*>(const_cast<fixed64*>(p));
-  const longlong2 a = q[0], b = q[1];
-  q[0] = make_longlong2(0, 0);
-  q[1] = make_longlong2(0, 0);
-  v[0] = fixed_to_float(a.x); v[1] = fixed_to_float(a.y);
-  v[2] = fixed_to_float(b.x); v[3] = fixed_to_float(b.y);
-}
-template <typename T>
-__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
-template <>
-__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-template <>
-__device__ __forceinline__ void store4<bf16>(bf16* p, const float (&v)[4]) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-  uint2 t;
-  t.x = *reinterpret_cast<uint32_t*>(&a);
-  t.y = *reinterpret_cast<uint32_t*>(&b);
-  *reinterpret_cast<uint2*>(p) = t;
-}
-
 // V = 4 or 8 elements at a time (8: two groups of four for float, one 16-byte vector for bfloat16)
 template <typename T, int V>
 __device__ __forceinline__ void loadv(const T* p, float (&v)[V]) {

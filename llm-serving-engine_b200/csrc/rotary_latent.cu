@@ -12,6 +12,8 @@
 //
 // Norms, angles, rotations, sigmoids and activations are float32 arithmetic whatever the types
 // of the tensors are.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -81,46 +83,68 @@ latent_rope_write_kernel(const TIn* __restrict__ proj, long long stride, int q_c
   }
 }
 
-// One warp per (token, head). q row: heads of (D + Dr) dims, the last Dr to be rotated. out row:
-// heads of Rp dims; dims [R, R + Dr) receive the rotated part, [R + Dr, Rp) zeros. Dims [0, R) are
-// written by the per-head product that runs beside this kernel.
-constexpr int LQR_WARPS = 4;
-
+// One thread per (token, head, two neighbouring dims behind the head's latent-space query). q row:
+// heads of (D + Dr) dims, the last Dr to be rotated. out row: heads of Rp dims; dims [R, R + Dr)
+// receive the rotated part, [R + Dr, Rp) zeros. Dims [0, R) are written by the per-head product
+// that runs beside this kernel.
 template <typename T>
-__global__ void __launch_bounds__(LQR_WARPS * 32)
+__global__ void __launch_bounds__(256)
 latent_query_rope_kernel(const T* __restrict__ q, int H, int D, int Dr, int rot,
                          const float* __restrict__ cos, const float* __restrict__ sin,
-                         const int* __restrict__ positions, T* __restrict__ out, int R, int Rp) {
+                         const int* __restrict__ positions, T* __restrict__ out, int R, int Rp,
+                         int pairs, long long total) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  extern __shared__ float qr_all[];  // [LQR_WARPS][Dr]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x, h = blockIdx.y * LQR_WARPS + warp;
-  if (h >= H) return;
-  float* qr = qr_all + warp * Dr;
-  const T* src = q + ((size_t)t * H + h) * (D + Dr) + D;
-  for (int i = lane; i < Dr; i += 32) qr[i] = Num<T>::to_float(src[i]);
-  __syncwarp();
-  const int pos = positions[t];
-  const float* cr = cos + (size_t)pos * (rot / 2);
-  const float* sr = sin + (size_t)pos * (rot / 2);
-  T* dst = out + ((size_t)t * H + h) * Rp + R;
-  for (int i = lane; i < Rp - R; i += 32)
-    dst[i] = Num<T>::from_float(i < Dr ? rotated_neighbour(qr, i, rot, cr, sr) : 0.f);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int p = (int)(idx % pairs);
+  const long long th = idx / pairs;  // token * H + head
+  const int i = 2 * p, n = Rp - R;
+  const T* src = q + th * (D + Dr) + D;
+  T* dst = out + th * Rp + R;
+  if (i < rot) {  // rot is even: the pair's second dim is inside too
+    const int pos = positions[th / H];
+    const float c = cos[(size_t)pos * (rot / 2) + p], sn = sin[(size_t)pos * (rot / 2) + p];
+    const float u = Num<T>::to_float(src[i]), v = Num<T>::to_float(src[i + 1]);
+    dst[i] = Num<T>::from_float(u * c - v * sn);
+    dst[i + 1] = Num<T>::from_float(v * c + u * sn);
+    return;
+  }
+  dst[i] = i < Dr ? src[i] : Num<T>::from_float(0.f);
+  if (i + 1 < n) dst[i + 1] = i + 1 < Dr ? src[i + 1] : Num<T>::from_float(0.f);
 }
 
-template <typename T, typename TG>
+// VEC4: four neighbouring columns of a row per thread (N a multiple of 4, o 16-byte aligned).
+template <typename T, typename TG, bool VEC4>
 __global__ void __launch_bounds__(256)
 sigmoid_gate_mul_kernel(T* __restrict__ o, const TG* __restrict__ g, long long g_stride, int col0,
                         int group, int N, long long total) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC4 ? 4 : 1);
   if (i >= total) return;
   const long long t = i / N;
   const int c = (int)(i - t * N);
-  const float z = Num<TG>::to_float(g[t * g_stride + col0 + c / group]);
-  o[i] = Num<T>::from_float(Num<T>::to_float(o[i]) / (1.f + expf(-z)));
+  const TG* gr = g + t * g_stride + col0;
+  if (VEC4) {
+    float v[4];
+    load4<T>(o + i, v);
+    int last = -1;
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gi = (c + j) / group;
+      if (gi != last) {
+        s = 1.f / (1.f + expf(-Num<TG>::to_float(gr[gi])));
+        last = gi;
+      }
+      v[j] *= s;
+    }
+    store4<T>(o + i, v);
+  } else {
+    const float z = Num<TG>::to_float(gr[c / group]);
+    o[i] = Num<T>::from_float(Num<T>::to_float(o[i]) / (1.f + expf(-z)));
+  }
 }
 
 __device__ __forceinline__ float plain_activation(float z, int act) {
@@ -135,15 +159,25 @@ __device__ __forceinline__ float plain_activation(float z, int act) {
   }
 }
 
-template <typename TIn, typename T>
+// VEC4: four elements per thread (total a multiple of 4, both tensors 16-byte aligned). Fixed-point
+// sums are taken as they are read: zeros are left behind for the next sums.
+template <typename TIn, typename T, bool VEC4>
 __global__ void __launch_bounds__(256)
-act_rows_kernel(const TIn* __restrict__ in, T* __restrict__ out, long long total, int act, int clear) {
+act_rows_kernel(const TIn* __restrict__ in, T* __restrict__ out, long long total, int act) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC4 ? 4 : 1);
   if (i >= total) return;
-  out[i] = Num<T>::from_float(plain_activation(Num<TIn>::to_float(in[i]), act));
-  if (clear) const_cast<TIn*>(in)[i] = Num<TIn>::from_float(0.f);  // fixed-point sums are left zero
+  if (VEC4) {
+    float v[4];
+    load4<TIn>(in + i, v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = plain_activation(v[j], act);
+    store4<T>(out + i, v);
+  } else {
+    out[i] = Num<T>::from_float(plain_activation(Num<TIn>::to_float(in[i]), act));
+    if (std::is_same<TIn, fixed64>::value) const_cast<TIn*>(in)[i] = Num<TIn>::from_float(0.f);
+  }
 }
 
 }  // namespace lse
@@ -184,15 +218,16 @@ extern "C" int lse_latent_query_rope(const void* q, int dtype, int T, int H, int
   if (D < 0 || Dr < 0 || rot < 0 || rot > Dr || rot % 2 || Rp < R + Dr || (rot > 0 && (!cos || !sin)))
     return LSE_BAD_ARGUMENT;
   if (Rp == R) return LSE_OK;
-  const dim3 grid(T, (H + LQR_WARPS - 1) / LQR_WARPS);
-  if (grid.y > 65535) return LSE_BAD_ARGUMENT;
-  const size_t smem = (size_t)LQR_WARPS * (Dr > 0 ? Dr : 1) * sizeof(float);
+  const int pairs = (Rp - R + 1) / 2;
+  const long long total = (long long)T * H * pairs;
+  const long long nblocks = (total + 255) / 256;
+  if (nblocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
   if (dtype == LSE_F32)
-    launch(latent_query_rope_kernel<float>, grid, LQR_WARPS * 32, smem, stream, (const float*)q, H, D, Dr, rot, cos,
-           sin, positions, (float*)out, R, Rp);
+    launch(latent_query_rope_kernel<float>, (unsigned)nblocks, 256, 0, stream, (const float*)q, H, D, Dr, rot, cos,
+           sin, positions, (float*)out, R, Rp, pairs, total);
   else if (dtype == LSE_BF16)
-    launch(latent_query_rope_kernel<bf16>, grid, LQR_WARPS * 32, smem, stream, (const bf16*)q, H, D, Dr, rot, cos,
-           sin, positions, (bf16*)out, R, Rp);
+    launch(latent_query_rope_kernel<bf16>, (unsigned)nblocks, 256, 0, stream, (const bf16*)q, H, D, Dr, rot, cos,
+           sin, positions, (bf16*)out, R, Rp, pairs, total);
   else return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
 }
@@ -202,14 +237,24 @@ extern "C" int lse_sigmoid_gate_mul(void* o, int dtype, const void* g, int g_dty
   if (T <= 0 || N <= 0) return LSE_OK;
   if (group <= 0 || col0 < 0) return LSE_BAD_ARGUMENT;
   const long long total = (long long)T * N;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const bool vec = N % 4 == 0 && reinterpret_cast<uintptr_t>(o) % 16 == 0;
+  const long long nblocks = ((vec ? total / 4 : total) + 255) / 256;
+  if (nblocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)nblocks;
+#define LSE_SGM_V(T_, TG, V) \
+  launch(sigmoid_gate_mul_kernel<T_, TG, V>, blocks, 256, 0, stream, (T_*)o, (const TG*)g, g_stride, col0, group, N, \
+         total)
 #define LSE_SGM(T_, TG) \
-  launch(sigmoid_gate_mul_kernel<T_, TG>, blocks, 256, 0, stream, (T_*)o, (const TG*)g, g_stride, col0, group, N, total)
+  do { \
+    if (vec) LSE_SGM_V(T_, TG, true); \
+    else LSE_SGM_V(T_, TG, false); \
+  } while (0)
   if (dtype == LSE_F32 && g_dtype == LSE_F32) LSE_SGM(float, float);
   else if (dtype == LSE_BF16 && g_dtype == LSE_F32) LSE_SGM(bf16, float);
   else if (dtype == LSE_BF16 && g_dtype == LSE_BF16) LSE_SGM(bf16, bf16);
   else return LSE_BAD_ARGUMENT;
 #undef LSE_SGM
+#undef LSE_SGM_V
   return LSE_CHECK_LAUNCH();
 }
 
@@ -217,14 +262,24 @@ extern "C" int lse_act_rows(const void* in, int in_dtype, void* out, int dtype, 
                             cudaStream_t stream) {
   if (total <= 0) return LSE_OK;
   if (act < 0 || act > 3) return LSE_BAD_ARGUMENT;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-#define LSE_ACT(TIn, T_, clear) \
-  launch(act_rows_kernel<TIn, T_>, blocks, 256, 0, stream, (const TIn*)in, (T_*)out, total, act, clear)
-  if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ACT(float, float, 0);
-  else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ACT(float, bf16, 0);
-  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ACT(bf16, bf16, 0);
-  else if (in_dtype == LSE_FIXED64 && dtype == LSE_BF16) LSE_ACT(fixed64, bf16, 1);
+  const bool vec = total % 4 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  const long long nblocks = ((vec ? total / 4 : total) + 255) / 256;
+  if (nblocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)nblocks;
+#define LSE_ACT_V(TIn, T_, V) \
+  launch(act_rows_kernel<TIn, T_, V>, blocks, 256, 0, stream, (const TIn*)in, (T_*)out, total, act)
+#define LSE_ACT(TIn, T_) \
+  do { \
+    if (vec) LSE_ACT_V(TIn, T_, true); \
+    else LSE_ACT_V(TIn, T_, false); \
+  } while (0)
+  if (in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ACT(float, float);
+  else if (in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ACT(float, bf16);
+  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ACT(bf16, bf16);
+  else if (in_dtype == LSE_FIXED64 && dtype == LSE_BF16) LSE_ACT(fixed64, bf16);
   else return LSE_BAD_ARGUMENT;
 #undef LSE_ACT
+#undef LSE_ACT_V
   return LSE_CHECK_LAUNCH();
 }

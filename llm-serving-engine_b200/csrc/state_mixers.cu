@@ -56,21 +56,28 @@ __global__ void token_shift_kernel(const float* __restrict__ x, const float* __r
 
 // ------------------------------------------------------------------------------------ x += norm(branch)
 // One block per row. y = a, or, with inner weights, ca * wa * a / rms(a) (+ cb * wb * b / rms(b));
-// then x += w * y / rms(y), and out = x in the compute dtype if out is given. y is recomputed
-// in the last pass rather than kept: the row's second read comes from cache. SUMS: a (and b) are
-// the fixed-point sums of a few-rows product; they are taken once (converted into shared memory,
-// zeros left behind) and read from there.
-template <typename TO, bool SUMS>
+// then x += w * y / rms(y). out (if given) = the new x in the compute dtype, or, with then_w, the
+// next norm of the new x: then_w * x / rms(x), while the block still holds the row. y is
+// recomputed in the last pass rather than kept: the row's second read comes from cache, and a
+// thread reads back only what it wrote itself. SUMS: a (and b) are the fixed-point sums of a
+// few-rows product; they are taken once (converted into shared memory, zeros left behind) and read
+// from there. V: elements per thread and visit (4: H a multiple of 4, every row 16-byte aligned).
+template <typename TO, bool SUMS, int V>
 __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const void* b,
                                    const float* __restrict__ wa,
                                    const float* __restrict__ wb, float ca, float cb, float eps_in,
                                    const float* __restrict__ w, float eps, TO* __restrict__ out,
-                                   int H) {
+                                   const float* __restrict__ then_w, float then_eps, int H) {
   __shared__ float scratch[32];
-  extern __shared__ float taken[];  // SUMS: [H] for a, then [H] for b
+  extern __shared__ __align__(16) float taken[];  // SUMS: [H] for a, then [H] for b
   pdl_trigger();
   pdl_wait();
   const size_t row = (size_t)blockIdx.x * H;
+  const int first = threadIdx.x * V, step = blockDim.x * V;
+  auto ld = [](const float* p, float (&v)[V]) {
+    if constexpr (V == 4) load4<float>(p, v);
+    else v[0] = p[0];
+  };
   const float* ar;
   const float* br = nullptr;
   if (SUMS) {
@@ -94,12 +101,16 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const v
   float inv_a = 1.f, inv_b = 1.f;
   if (wa) {
     float sa = 0.f, sb = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      const float va = ar[i];
-      sa += va * va;
+    for (int i = first; i < H; i += step) {
+      float va[V];
+      ld(ar + i, va);
+#pragma unroll
+      for (int j = 0; j < V; ++j) sa += va[j] * va[j];
       if (br) {
-        const float vb = br[i];
-        sb += vb * vb;
+        float vb[V];
+        ld(br + i, vb);
+#pragma unroll
+        for (int j = 0; j < V; ++j) sb += vb[j] * vb[j];
       }
     }
     sa = block_sum(sa, scratch);
@@ -109,24 +120,60 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const v
       inv_b = cb * rsqrtf(sb / (float)H + eps_in);
     }
   }
-  auto y_at = [&](int i) -> float {
-    if (!wa) return ar[i];
-    float y = ar[i] * inv_a * wa[i];
-    if (br) y += br[i] * inv_b * wb[i];
-    return y;
+  auto y_at = [&](int i, float (&y)[V]) {
+    ld(ar + i, y);
+    if (!wa) return;
+    float wv[V];
+    ld(wa + i, wv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) y[j] *= inv_a * wv[j];
+    if (br) {
+      float vb[V];
+      ld(br + i, vb);
+      ld(wb + i, wv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) y[j] += vb[j] * inv_b * wv[j];
+    }
+  };
+  auto put = [&](int i, const float (&v)[V]) {
+    if constexpr (V == 4) store4<TO>(out + row + i, v);
+    else out[row + i] = Num<TO>::from_float(v[0]);
   };
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float y = y_at(i);
-    ss += y * y;
+  for (int i = first; i < H; i += step) {
+    float y[V];
+    y_at(i, y);
+#pragma unroll
+    for (int j = 0; j < V; ++j) ss += y[j] * y[j];
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)H + eps);
   float* xr = x + row;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = xr[i] + y_at(i) * inv * w[i];
-    xr[i] = v;
-    if (out) out[row + i] = Num<TO>::from_float(v);
+  float s2 = 0.f;
+  for (int i = first; i < H; i += step) {
+    float y[V], xv[V], wv[V];
+    y_at(i, y);
+    ld(xr + i, xv);
+    ld(w + i, wv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      xv[j] += y[j] * inv * wv[j];
+      s2 += xv[j] * xv[j];
+    }
+    if constexpr (V == 4) store4<float>(xr + i, xv);
+    else xr[i] = xv[0];
+    if (out && !then_w) put(i, xv);
+  }
+  if (!out || !then_w) return;
+  s2 = block_sum(s2, scratch);
+  const float inv2 = rsqrtf(s2 / (float)H + then_eps);
+  for (int i = first; i < H; i += step) {
+    float xv[V], wv[V];
+    ld(xr + i, xv);  // this thread's own writes
+    ld(then_w + i, wv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) xv[j] *= inv2 * wv[j];
+    put(i, xv);
   }
 }
 
@@ -620,23 +667,35 @@ extern "C" int lse_token_shift(const float* x, const float* mix, float* state, v
 
 extern "C" int lse_rmsnorm_add(float* x, const void* a, const void* b, int branch_dtype, const float* wa,
                                const float* wb, float ca, float cb, float eps_in, const float* w, float eps,
-                               void* out, int out_dtype, int T, int H, cudaStream_t stream) {
+                               void* out, int out_dtype, const float* then_w, float then_eps, int T, int H,
+                               cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (!x || !a || !w || (b && !wa) || (wa && b && !wb)) return LSE_BAD_ARGUMENT;
   if (branch_dtype != LSE_F32 && branch_dtype != LSE_FIXED64) return LSE_BAD_ARGUMENT;
   const bool sums = branch_dtype == LSE_FIXED64;
   const size_t smem = sums ? (size_t)H * (b ? 2 : 1) * sizeof(float) : 0;
   if (smem > 48 * 1024) return LSE_BAD_ARGUMENT;
+  if (then_w && !out) return LSE_BAD_ARGUMENT;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const bool to_bf16 = out && out_dtype == LSE_BF16;
   if (!to_bf16 && out && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = H % 4 == 0 && aligned(x) && aligned(w) && aligned(out) && aligned(wa) && aligned(wb) &&
+                   aligned(then_w) && (sums || (aligned(a) && aligned(b)));
+#define LSE_RNA_V(TO, S, V) \
+  launch(rmsnorm_add_kernel<TO, S, V>, T, threads, smem, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps, (TO*)out, \
+         then_w, then_eps, H)
 #define LSE_RNA(TO, S) \
-  launch(rmsnorm_add_kernel<TO, S>, T, threads, smem, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps, (TO*)out, H)
+  do { \
+    if (vec) LSE_RNA_V(TO, S, 4); \
+    else LSE_RNA_V(TO, S, 1); \
+  } while (0)
   if (to_bf16) {
     if (sums) LSE_RNA(bf16, true); else LSE_RNA(bf16, false);
   } else {
     if (sums) LSE_RNA(float, true); else LSE_RNA(float, false);
   }
+#undef LSE_RNA_V
 #undef LSE_RNA
   return LSE_CHECK_LAUNCH();
 }

@@ -642,10 +642,14 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None):
+    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None, then_weight=None, then_eps=0.0):
         """``x += weight * y / rms(y)`` with ``y`` the branch (a float32 tensor, or a
         ``BranchMix`` whose members are normed and summed in the same launch); returns the new
-        ``x`` in ``out_dtype`` unless that is None."""
+        ``x`` in ``out_dtype`` unless that is None. With ``then_weight`` what is returned is the
+        next norm of the new ``x``, ``then_weight * x / rms(x)`` (eps ``then_eps``), from the same
+        launch."""
+        if then_weight is not None and out_dtype is None:
+            raise ValueError("the norm that follows needs an output dtype")
         out = None if out_dtype is None else torch.empty(x.shape, dtype=out_dtype, device=x.device)
         members = list(branch.branches) if hasattr(branch, "branches") else [branch]
         # products still lying as sums are taken by the kernel itself if all members are such
@@ -656,9 +660,11 @@ class CudaOps:
         tensors = [(m.sums if take else m.resolve()) if isinstance(m, DeferredProduct) else m for m in members]
         if hasattr(branch, "branches"):
             a, b, wa, wb, ca, cb = self._two_branches(tensors, branch.weights, branch.coefficients)
-            self.ext.rmsnorm_add(x, a, b, wa, wb, ca, cb, float(branch.eps), weight, float(eps), out)
+            self.ext.rmsnorm_add(x, a, b, wa, wb, ca, cb, float(branch.eps), weight, float(eps), out,
+                                 then_weight, float(then_eps))
         else:
-            self.ext.rmsnorm_add(x, tensors[0], None, None, None, 1.0, 0.0, 0.0, weight, float(eps), out)
+            self.ext.rmsnorm_add(x, tensors[0], None, None, None, 1.0, 0.0, 0.0, weight, float(eps), out,
+                                 then_weight, float(then_eps))
         self.launches += 1
         if take:
             for m in deferred:

@@ -321,6 +321,28 @@ def project_into(ops, a, w, bias, out_dtype, residual, may_defer: bool = False):
     return ops.linear(a, w, bias, out_dtype=out_dtype, accumulate_into=residual)
 
 
+class PendingNormedBranch:
+    """A branch's output that is still to be normed by ``norm`` and added to ``x``: what a block
+    whose last step is ``x += norm(branch)`` may hand on instead of doing it, so that the norm
+    which reads ``x`` next does both while it holds the rows (``Norm.add_normed_then``). Exactly
+    one of :meth:`take` (by that norm) and :meth:`resolve` (the sum is formed now) happens before
+    anything else reads ``x``."""
+
+    __slots__ = ("norm", "x", "branch")
+
+    def __init__(self, norm: "Norm", x, branch) -> None:
+        self.norm, self.x, self.branch = norm, x, branch
+
+    def take(self):
+        branch, self.branch = self.branch, None
+        return branch
+
+    def resolve(self) -> None:
+        if self.branch is not None:
+            self.norm.add_normed(self.x, self.take(), emit=False)
+        return None
+
+
 def settle(pending, norm):
     """What ``norm`` can take as its ``residual``: pending sums are handed on only to a norm that
     declares ``takes_pending_sums``; for any other they are added now."""

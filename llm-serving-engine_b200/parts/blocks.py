@@ -28,7 +28,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any
 
-from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, count_states, flatten_needs, has_pages, settle
+from .base import (BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, PendingNormedBranch, count_states,
+                   flatten_needs, has_pages, settle)
 
 
 @dataclass(frozen=True)
@@ -164,13 +165,11 @@ class SandwichBlock(Block):
         else:
             a = self.mixer.forward(h, step, cache)
         if self.feed_forward is None:
-            self.norm_mixer_out.add_normed(x, a, emit=False)
-            return x, None
+            return x, PendingNormedBranch(self.norm_mixer_out, x, a)  # the next norm adds it as it reads x
         # x += norm(a), and the next norm of the new x, in the norm's own way (one launch if it can)
         h = self.norm_mixer_out.add_normed_then(x, a, self.norm_post)
         if getattr(self.feed_forward, "accepts_residual", False):
             f = self.feed_forward.forward(h, step, may_defer=True)
         else:
             f = self.feed_forward.forward(h, step)
-        self.norm_ff_out.add_normed(x, f, emit=False)
-        return x, None
+        return x, PendingNormedBranch(self.norm_ff_out, x, f)

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from .base import NORMS, Norm, ParamDecl
+from .base import NORMS, Norm, ParamDecl, PendingNormedBranch
 
 
 @dataclass(frozen=True)
@@ -35,6 +35,10 @@ class RMSNorm(Norm):
         self.weight = (w + 1.0) if self.spec.unit_offset else w
 
     def forward(self, x, residual=None, rows=None):
+        if isinstance(residual, PendingNormedBranch):
+            if rows is None:  # the branch's norm, the sum and this norm while the rows are held once
+                return residual.norm.add_normed_then(x, residual.take(), self)
+            residual = residual.resolve()  # only some rows are read here: the whole sum is formed first
         return self.ops.add_rmsnorm(
             x, residual, self.weight, self.spec.eps, out_dtype=self.env.dtype, rows=rows
         )
@@ -43,3 +47,9 @@ class RMSNorm(Norm):
         """``x += norm(branch)``; returns the new ``x`` in the compute dtype if ``emit``."""
         return self.ops.rmsnorm_add(x, branch, self.weight, self.spec.eps,
                                     out_dtype=self.env.dtype if emit else None)
+
+    def add_normed_then(self, x, branch, then):
+        if not isinstance(then, RMSNorm):
+            return super().add_normed_then(x, branch, then)
+        return self.ops.rmsnorm_add(x, branch, self.weight, self.spec.eps, out_dtype=self.env.dtype,
+                                    then_weight=then.weight, then_eps=then.spec.eps)

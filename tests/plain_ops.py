@@ -342,10 +342,14 @@ class PlainOps:
             y = y + c * (a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps) * w)
         return y
 
-    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None):
+    def rmsnorm_add(self, x, branch, weight, eps, out_dtype=None, then_weight=None, then_eps=0.0):
         y = branch.resolve() if hasattr(branch, "resolve") else branch.float()
         x += y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight
-        return None if out_dtype is None else x.to(out_dtype)
+        if out_dtype is None:
+            return None
+        if then_weight is not None:
+            return (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + then_eps) * then_weight).to(out_dtype)
+        return x.to(out_dtype)
 
     def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
                                activation, key_scale, cos, sin):
