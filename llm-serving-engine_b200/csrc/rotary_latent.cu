@@ -83,67 +83,91 @@ latent_rope_write_kernel(const TIn* __restrict__ proj, long long stride, int q_c
   }
 }
 
-// One thread per (token, head, two neighbouring dims behind the head's latent-space query). q row:
-// heads of (D + Dr) dims, the last Dr to be rotated. out row: heads of Rp dims; dims [R, R + Dr)
-// receive the rotated part, [R + Dr, Rp) zeros. Dims [0, R) are written by the per-head product
-// that runs beside this kernel.
-template <typename T>
+// A token per blockIdx.x; one thread per (head, two neighbouring dims behind the head's
+// latent-space query). q row: heads of (D + Dr) dims, the last Dr to be rotated. out row: heads of
+// Rp dims; dims [R, R + Dr) receive the rotated part, [R + Dr, Rp) zeros. Dims [0, R) are written
+// by the per-head product that runs beside this kernel. PAIRS: D, Dr, R and Rp are even, so that a
+// pair is one aligned 4- or 8-byte access on both sides.
+template <typename T, bool PAIRS>
 __global__ void __launch_bounds__(256)
 latent_query_rope_kernel(const T* __restrict__ q, int H, int D, int Dr, int rot,
                          const float* __restrict__ cos, const float* __restrict__ sin,
                          const int* __restrict__ positions, T* __restrict__ out, int R, int Rp,
-                         int pairs, long long total) {
+                         int pairs) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const int p = (int)(idx % pairs);
-  const long long th = idx / pairs;  // token * H + head
+  const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+  if (idx >= H * pairs) return;
+  const int h = idx / pairs, p = idx - h * pairs;
+  const size_t th = (size_t)blockIdx.x * H + h;
   const int i = 2 * p, n = Rp - R;
-  const T* src = q + th * (D + Dr) + D;
-  T* dst = out + th * Rp + R;
-  if (i < rot) {  // rot is even: the pair's second dim is inside too
-    const int pos = positions[th / H];
-    const float c = cos[(size_t)pos * (rot / 2) + p], sn = sin[(size_t)pos * (rot / 2) + p];
-    const float u = Num<T>::to_float(src[i]), v = Num<T>::to_float(src[i + 1]);
-    dst[i] = Num<T>::from_float(u * c - v * sn);
-    dst[i + 1] = Num<T>::from_float(v * c + u * sn);
-    return;
+  const T* src = q + th * (D + Dr) + D + i;
+  T* dst = out + th * Rp + R + i;
+  float u = 0.f, v = 0.f;
+  if (PAIRS) {
+    if (i < Dr) {  // Dr is even: the pair's second dim is inside too
+      if constexpr (sizeof(T) == 2) {
+        const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(src);
+        u = __low2float(t);
+        v = __high2float(t);
+      } else {
+        const float2 t = *reinterpret_cast<const float2*>(src);
+        u = t.x;
+        v = t.y;
+      }
+    }
+  } else {
+    if (i < Dr) u = Num<T>::to_float(src[0]);
+    if (i + 1 < Dr) v = Num<T>::to_float(src[1]);
   }
-  dst[i] = i < Dr ? src[i] : Num<T>::from_float(0.f);
-  if (i + 1 < n) dst[i + 1] = i + 1 < Dr ? src[i + 1] : Num<T>::from_float(0.f);
+  if (i < rot) {  // rot is even and at most Dr
+    const size_t at = (size_t)positions[blockIdx.x] * (rot / 2) + p;
+    const float c = cos[at], sn = sin[at];
+    const float ru = u * c - v * sn;
+    v = v * c + u * sn;
+    u = ru;
+  }
+  if (PAIRS) {
+    if constexpr (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(u, v);
+    else *reinterpret_cast<float2*>(dst) = make_float2(u, v);
+  } else {
+    dst[0] = Num<T>::from_float(u);
+    if (i + 1 < n) dst[1] = Num<T>::from_float(v);
+  }
 }
 
-// VEC4: four neighbouring columns of a row per thread (N a multiple of 4, o 16-byte aligned).
+// A row per blockIdx.x, the row's columns over blockIdx.y and the threads. VEC4: four neighbouring
+// columns per thread (N a multiple of 4, o 16-byte aligned).
 template <typename T, typename TG, bool VEC4>
 __global__ void __launch_bounds__(256)
 sigmoid_gate_mul_kernel(T* __restrict__ o, const TG* __restrict__ g, long long g_stride, int col0,
-                        int group, int N, long long total) {
+                        int group, int N) {
   pdl_trigger();
   pdl_wait();  // everything below reads what kernels before this one wrote
-  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC4 ? 4 : 1);
-  if (i >= total) return;
-  const long long t = i / N;
-  const int c = (int)(i - t * N);
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * (VEC4 ? 4 : 1);
+  if (c >= N) return;
+  const size_t t = blockIdx.x;
   const TG* gr = g + t * g_stride + col0;
+  T* op = o + t * N + c;
+  int gi = c / group;
   if (VEC4) {
     float v[4];
-    load4<T>(o + i, v);
-    int last = -1;
-    float s = 0.f;
+    load4<T>(op, v);
+    int left = group - (c - gi * group);  // columns of this thread's first gate that are still to come
+    float sg = 1.f / (1.f + expf(-Num<TG>::to_float(gr[gi])));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int gi = (c + j) / group;
-      if (gi != last) {
-        s = 1.f / (1.f + expf(-Num<TG>::to_float(gr[gi])));
-        last = gi;
+      if (left == 0) {
+        sg = 1.f / (1.f + expf(-Num<TG>::to_float(gr[++gi])));
+        left = group;
       }
-      v[j] *= s;
+      v[j] *= sg;
+      --left;
     }
-    store4<T>(o + i, v);
+    store4<T>(op, v);
   } else {
-    const float z = Num<TG>::to_float(gr[c / group]);
-    o[i] = Num<T>::from_float(Num<T>::to_float(o[i]) / (1.f + expf(-z)));
+    const float z = Num<TG>::to_float(gr[gi]);
+    *op = Num<T>::from_float(Num<T>::to_float(*op) / (1.f + expf(-z)));
   }
 }
 
@@ -219,16 +243,21 @@ extern "C" int lse_latent_query_rope(const void* q, int dtype, int T, int H, int
     return LSE_BAD_ARGUMENT;
   if (Rp == R) return LSE_OK;
   const int pairs = (Rp - R + 1) / 2;
-  const long long total = (long long)T * H * pairs;
-  const long long nblocks = (total + 255) / 256;
-  if (nblocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
-  if (dtype == LSE_F32)
-    launch(latent_query_rope_kernel<float>, (unsigned)nblocks, 256, 0, stream, (const float*)q, H, D, Dr, rot, cos,
-           sin, positions, (float*)out, R, Rp, pairs, total);
-  else if (dtype == LSE_BF16)
-    launch(latent_query_rope_kernel<bf16>, (unsigned)nblocks, 256, 0, stream, (const bf16*)q, H, D, Dr, rot, cos,
-           sin, positions, (bf16*)out, R, Rp, pairs, total);
-  else return LSE_BAD_ARGUMENT;
+  const dim3 grid(T, (H * pairs + 255) / 256);
+  if (grid.y > 65535) return LSE_BAD_ARGUMENT;
+  const bool even = D % 2 == 0 && Dr % 2 == 0 && R % 2 == 0 && Rp % 2 == 0 &&
+                    reinterpret_cast<uintptr_t>(q) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0;
+#define LSE_LQR(T_, P) \
+  launch(latent_query_rope_kernel<T_, P>, grid, 256, 0, stream, (const T_*)q, H, D, Dr, rot, cos, sin, positions, \
+         (T_*)out, R, Rp, pairs)
+  if (dtype == LSE_F32) {
+    if (even) LSE_LQR(float, true); else LSE_LQR(float, false);
+  } else if (dtype == LSE_BF16) {
+    if (even) LSE_LQR(bf16, true); else LSE_LQR(bf16, false);
+  } else {
+    return LSE_BAD_ARGUMENT;
+  }
+#undef LSE_LQR
   return LSE_CHECK_LAUNCH();
 }
 
@@ -236,14 +265,12 @@ extern "C" int lse_sigmoid_gate_mul(void* o, int dtype, const void* g, int g_dty
                                     int col0, int group, int T, int N, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return LSE_OK;
   if (group <= 0 || col0 < 0) return LSE_BAD_ARGUMENT;
-  const long long total = (long long)T * N;
   const bool vec = N % 4 == 0 && reinterpret_cast<uintptr_t>(o) % 16 == 0;
-  const long long nblocks = ((vec ? total / 4 : total) + 255) / 256;
-  if (nblocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
-  const unsigned blocks = (unsigned)nblocks;
+  const int per_block = 256 * (vec ? 4 : 1);
+  const dim3 blocks(T, (N + per_block - 1) / per_block);
+  if (blocks.y > 65535) return LSE_BAD_ARGUMENT;
 #define LSE_SGM_V(T_, TG, V) \
-  launch(sigmoid_gate_mul_kernel<T_, TG, V>, blocks, 256, 0, stream, (T_*)o, (const TG*)g, g_stride, col0, group, N, \
-         total)
+  launch(sigmoid_gate_mul_kernel<T_, TG, V>, blocks, 256, 0, stream, (T_*)o, (const TG*)g, g_stride, col0, group, N)
 #define LSE_SGM(T_, TG) \
   do { \
     if (vec) LSE_SGM_V(T_, TG, true); \

@@ -62,7 +62,10 @@ __global__ void token_shift_kernel(const float* __restrict__ x, const float* __r
 // thread reads back only what it wrote itself. SUMS: a (and b) are the fixed-point sums of a
 // few-rows product; they are taken once (converted into shared memory, zeros left behind) and read
 // from there. V: elements per thread and visit (4: H a multiple of 4, every row 16-byte aligned).
-template <typename TO, bool SUMS, int V>
+// K > 0: a thread visits at most K places of the row and keeps y and the new x of each in
+// registers, so that a and x are read once and x's old values are already on their way while the
+// block sums the squares; K = 0: any row length, y recomputed and x read back.
+template <typename TO, bool SUMS, int V, int K>
 __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const void* b,
                                    const float* __restrict__ wa,
                                    const float* __restrict__ wb, float ca, float cb, float eps_in,
@@ -139,6 +142,55 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const v
     if constexpr (V == 4) store4<TO>(out + row + i, v);
     else out[row + i] = Num<TO>::from_float(v[0]);
   };
+  float* xr = x + row;
+  if constexpr (K > 0) {
+    float yk[K][V], xk[K][V];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int i = first + k * step;
+      if (i < H) {
+        y_at(i, yk[k]);
+        ld(xr + i, xk[k]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) ss += yk[k][j] * yk[k][j];
+      }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int i = first + k * step;
+      if (i < H) {
+        float wv[V];
+        ld(w + i, wv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          xk[k][j] += yk[k][j] * inv * wv[j];
+          s2 += xk[k][j] * xk[k][j];
+        }
+        if constexpr (V == 4) store4<float>(xr + i, xk[k]);
+        else xr[i] = xk[k][0];
+        if (out && !then_w) put(i, xk[k]);
+      }
+    }
+    if (!out || !then_w) return;
+    s2 = block_sum(s2, scratch);
+    const float inv2 = rsqrtf(s2 / (float)H + then_eps);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int i = first + k * step;
+      if (i < H) {
+        float wv[V];
+        ld(then_w + i, wv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) xk[k][j] *= inv2 * wv[j];
+        put(i, xk[k]);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = first; i < H; i += step) {
     float y[V];
@@ -148,7 +200,6 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const void* a, const v
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)H + eps);
-  float* xr = x + row;
   float s2 = 0.f;
   for (int i = first; i < H; i += step) {
     float y[V], xv[V], wv[V];
@@ -682,13 +733,18 @@ extern "C" int lse_rmsnorm_add(float* x, const void* a, const void* b, int branc
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = H % 4 == 0 && aligned(x) && aligned(w) && aligned(out) && aligned(wa) && aligned(wb) &&
                    aligned(then_w) && (sums || (aligned(a) && aligned(b)));
-#define LSE_RNA_V(TO, S, V) \
-  launch(rmsnorm_add_kernel<TO, S, V>, T, threads, smem, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps, (TO*)out, \
-         then_w, then_eps, H)
+  const int per_visit = threads * (vec ? 4 : 1);
+  const int visits = (H + per_visit - 1) / per_visit;  // places of the row per thread
+#define LSE_RNA_V(TO, S, V, K) \
+  launch(rmsnorm_add_kernel<TO, S, V, K>, T, threads, smem, stream, x, a, b, wa, wb, ca, cb, eps_in, w, eps, \
+         (TO*)out, then_w, then_eps, H)
 #define LSE_RNA(TO, S) \
   do { \
-    if (vec) LSE_RNA_V(TO, S, 4); \
-    else LSE_RNA_V(TO, S, 1); \
+    if (vec && visits == 1) LSE_RNA_V(TO, S, 4, 1); \
+    else if (vec && visits == 2) LSE_RNA_V(TO, S, 4, 2); \
+    else if (vec) LSE_RNA_V(TO, S, 4, 0); \
+    else if (visits == 1) LSE_RNA_V(TO, S, 1, 1); \
+    else LSE_RNA_V(TO, S, 1, 0); \
   } while (0)
   if (to_bf16) {
     if (sums) LSE_RNA(bf16, true); else LSE_RNA(bf16, false);

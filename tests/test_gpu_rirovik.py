@@ -150,7 +150,7 @@ def test_sigmoid_gate(ops, dtype, gdtype, T, N, group, col0, extra):
     close(got, o.to(F) * torch.sigmoid(g.to(F)[:, cols]), 2e-6 if dtype == torch.float32 else 5e-3)
 
 
-@pytest.mark.parametrize("H", [70, 96, 2052])
+@pytest.mark.parametrize("H", [70, 96, 131, 2052, 4100])
 @pytest.mark.parametrize("emit", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("sums", [False, True])
 def test_a_branchs_norm_the_sum_and_the_next_norm_in_one_launch(ops, H, emit, sums):
