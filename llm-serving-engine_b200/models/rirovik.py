@@ -1,7 +1,7 @@
 """The Rirovik architecture as data: which parts each layer has and where its tensors come from.
 
 The embedded token is its row of the embedding table times a constant. Every layer is a
-``sandwich`` block (a norm before and after each sublayer, all with weights stored around zero).
+``sandwich`` block (a norm before and after each sublayer, each multiplying by one plus its stored weight).
 The mixer is one of
 
 * latent attention with a query latent, a rotated key part that all heads share, a window and a

@@ -24,7 +24,7 @@ and reads the rows that layer wrote, with its own ``Wuk``, ``Wuv``, queries, win
 Further options of the spec, all off by default (any of them takes the layer through
 ``_forward_rotary``):
 
-* ``query_rank``: queries go through a latent of their own, ``q = Wuq (w_q * d_q / rms(d_q))``,
+* ``query_rank``: the queries are made from a latent of their own, ``q = Wuq (w_q * d_q / rms(d_q))``,
   ``d_q = Wdq h``;
 * ``rope_dim``: beside its ``head_dim`` dims every query head has ``rope_dim`` more (laid out
   behind them), which meet one key part of ``rope_dim`` dims that all heads share: the last
@@ -33,8 +33,8 @@ Further options of the spec, all off by default (any of them takes the layer thr
   rope_rotated)``). The score is ``scale * (q . k_j + q_rope . k_rope_j)``. The cache row of a token
   is ``[c | k_rope (turned)]``; on the query's side ``[Wuk^T q | q_rope]`` meets it, and ``Wuv``
   has zero columns where the key part lies;
-* ``gate="head"``: head h's output is multiplied by ``sigmoid(Wg h)_h``, one row of ``Wg`` per
-  head, reading the mixer's input.
+* ``gate="head"``: a factor per head on the heads' outputs, ``sigmoid(Wg x)[head]`` with ``x`` the
+  mixer's input and one row of ``Wg`` per head.
 
 The rows of the fused input matrix: the queries' (``Wq``, or ``Wdq`` with ``query_rank``), then
 the latent's with the key part's behind them (a layer with a latent of its own), then the gate's.

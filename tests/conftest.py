@@ -348,7 +348,7 @@ def write_rirovik(folder, name):
     for k, v in t.items():
         if k.endswith("dq.norm") or k.endswith("dkv.norm"):
             t[k] = (1.0 + (torch.rand(v.shape, generator=g) - 0.5)).to(v.dtype)
-        elif v.dim() == 1:  # norms stored around zero, biases
+        elif v.dim() == 1:  # norm offsets, biases
             t[k] = (torch.rand(v.shape, generator=g) - 0.5).to(v.dtype)
         elif k == "embed":
             t[k] = (v.float() * 40 / spec["config"]["embedding"]["scale"]).to(v.dtype)
