@@ -136,6 +136,41 @@ latent_query_rope_kernel(const T* __restrict__ q, int H, int D, int Dr, int rot,
   }
 }
 
+// The same for bfloat16 rows whose pieces (D, Dr, rot, R, Rp) are all multiples of 8: one thread per
+// (head, 16-byte vector of eight dims), which is rotated whole, copied whole or zero.
+__global__ void __launch_bounds__(256)
+latent_query_rope_wide_kernel(const bf16* __restrict__ q, int H, int D, int Dr, int rot,
+                              const float* __restrict__ cos, const float* __restrict__ sin,
+                              const int* __restrict__ positions, bf16* __restrict__ out, int R, int Rp,
+                              int vectors) {
+  pdl_trigger();
+  pdl_wait();  // everything below reads what kernels before this one wrote
+  const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+  if (idx >= H * vectors) return;
+  const int h = idx / vectors, i = 8 * (idx - h * vectors);
+  const size_t th = (size_t)blockIdx.x * H + h;
+  Vec16<bf16> v;
+  if (i < Dr) {
+    v = load16(q + th * (D + Dr) + D + i);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v.v[j] = __float2bfloat16_rn(0.f);
+  }
+  if (i < rot) {
+    const size_t at = (size_t)positions[blockIdx.x] * (rot / 2) + i / 2;
+    float c[4], sn[4];
+    load4<float>(cos + at, c);
+    load4<float>(sin + at, sn);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float u = __bfloat162float(v.v[2 * p]), w = __bfloat162float(v.v[2 * p + 1]);
+      v.v[2 * p] = __float2bfloat16_rn(u * c[p] - w * sn[p]);
+      v.v[2 * p + 1] = __float2bfloat16_rn(w * c[p] + u * sn[p]);
+    }
+  }
+  store16(out + th * Rp + R + i, v);
+}
+
 // A row per blockIdx.x, the row's columns over blockIdx.y and the threads. VEC4: four neighbouring
 // columns per thread (N a multiple of 4, o 16-byte aligned).
 template <typename T, typename TG, bool VEC4>
@@ -247,6 +282,16 @@ extern "C" int lse_latent_query_rope(const void* q, int dtype, int T, int H, int
   if (grid.y > 65535) return LSE_BAD_ARGUMENT;
   const bool even = D % 2 == 0 && Dr % 2 == 0 && R % 2 == 0 && Rp % 2 == 0 &&
                     reinterpret_cast<uintptr_t>(q) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0;
+  auto aligned16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (dtype == LSE_BF16 && D % 8 == 0 && Dr % 8 == 0 && rot % 8 == 0 && R % 8 == 0 && Rp % 8 == 0 &&
+      aligned16(q) && aligned16(out) && aligned16(cos) && aligned16(sin)) {
+    const int vectors = (Rp - R) / 8;
+    const dim3 wide(T, (H * vectors + 255) / 256);
+    if (wide.y > 65535) return LSE_BAD_ARGUMENT;
+    launch(latent_query_rope_wide_kernel, wide, 256, 0, stream, (const bf16*)q, H, D, Dr, rot, cos, sin, positions,
+           (bf16*)out, R, Rp, vectors);
+    return LSE_CHECK_LAUNCH();
+  }
 #define LSE_LQR(T_, P) \
   launch(latent_query_rope_kernel<T_, P>, grid, 256, 0, stream, (const T_*)q, H, D, Dr, rot, cos, sin, positions, \
          (T_*)out, R, Rp, pairs)

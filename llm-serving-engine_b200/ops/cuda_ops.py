@@ -385,6 +385,8 @@ class CudaOps:
         return q
 
     def attention_q_tile(self, dtype, head_dim):
+        if head_dim not in self._attn_loaded:  # a caller that did not announce its head size first
+            self.check_attention_shape(head_dim, dtype)
         return int(self.ext.attention_q_tile(head_dim, dtype == torch.bfloat16,
                                              self.attention_kernel))
 

@@ -106,7 +106,7 @@ def test_latent_rows_are_normed_turned_and_find_their_page(ops, dtype, Rq, R, Dr
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,H,D,Dr,rot,R", [(1, 3, 16, 8, 8, 40), (37, 5, 8, 4, 2, 22), (130, 8, 64, 32, 32, 128),
-                                            (70, 2, 20, 6, 6, 18), (9, 4, 24, 0, 0, 17)])
+                                            (70, 2, 20, 6, 6, 18), (9, 4, 24, 0, 0, 17), (5, 6, 16, 16, 8, 24), (3, 2, 8, 8, 0, 16)])
 def test_the_querys_side_scores_like_keys_per_head(ops, dtype, T, H, D, Dr, rot, R):
     """``[Wuk^T q | turned q_rot] . [c | k_rot]`` equals ``q . (Wuk c) + turned q_rot . k_rot``; the
     padding of a head's slot is zero whatever the buffer held."""
