@@ -108,6 +108,18 @@ def _register_builtin() -> None:
             checkpoint_layout=rirovik_checkpoint_layout,
         )
     )
+    from ..models.lanilorn import lanilorn_checkpoint_layout, lanilorn_plan
+    from .lanilorn import LanilornConfig
+
+    register_architecture(
+        Architecture(
+            name="Lanilorn",
+            model_type="lanilorn",
+            config_cls=LanilornConfig,
+            plan=lanilorn_plan,
+            checkpoint_layout=lanilorn_checkpoint_layout,
+        )
+    )
 
 
 _register_builtin()

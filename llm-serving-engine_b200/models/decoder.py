@@ -133,7 +133,9 @@ class DecoderModel:
     def forward(self, step, pools) -> torch.Tensor:
         """Run this step's tokens; return float32 logits ``[len(step.logit_rows), vocab]``."""
         x = self.ops.embedding(step.token_ids, self.embed_weight)
-        if self.plan.embed_scale != 1.0:
+        if self.plan.residual_streams > 1:  # every stream starts as the (scaled) embedded token
+            x = self.ops.streams_spread(x, self.plan.residual_streams, self.plan.embed_scale)
+        elif self.plan.embed_scale != 1.0:
             x *= self.plan.embed_scale
         if self.embed_terms:
             view, at = pools.view(self.embed_cache, writes=True), 0

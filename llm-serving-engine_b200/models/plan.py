@@ -36,6 +36,9 @@ class ModelPlan:
     embed_scale: float = 1.0  # the embedded tokens are multiplied by this
     logit_scale: float = 1.0  # the logits are multiplied by this ...
     logit_softcap: float = 0.0  # ... and then, if > 0, squashed to cap * tanh(logits / cap)
+    # copies of the embedded token that the blocks carry side by side (``streams`` blocks); the
+    # residual state is then [T, residual_streams * hidden_size] and the final norm reads all of it
+    residual_streams: int = 1
 
     def validate(self) -> None:
         if not self.run_order:

@@ -23,7 +23,10 @@ from .base import (
     role_dtype,
 )
 from .blocks import BranchNormBlock, BranchNormBlockSpec, PreNormBlock, PreNormBlockSpec, SandwichBlock, SandwichBlockSpec
-from .linear_attention import DecayLinearAttention, DecayLinearAttentionSpec
+from .linear_attention import (DecayLinearAttention, DecayLinearAttentionSpec, GatedLinearAttention,
+                               GatedLinearAttentionSpec)
+from .differential_attention import DifferentialAttention, DifferentialAttentionSpec
+from .streams import StreamsBlock, StreamsBlockSpec, StreamsRMSNorm, StreamsRMSNormSpec, StreamsWrite, StreamsWriteSpec
 from .parallel import ParallelMixer, ParallelMixerSpec
 from .token_shift import TokenShift, TokenShiftSpec
 from .feed_forward import MLP, MLPSpec, SwiGLU, SwiGLUSpec
@@ -42,4 +45,6 @@ __all__ = [
     "DecayLinearAttention", "DecayLinearAttentionSpec", "ParallelMixer", "ParallelMixerSpec", "TokenShift",
     "TokenShiftSpec", "HashedPairEmbedding", "HashedPairSpec", "LatentAttention", "LatentAttentionSpec",
     "RoutedExperts", "RoutedExpertsSpec", "SinusoidSpec", "SandwichBlock", "SandwichBlockSpec", "MLP", "MLPSpec",
+    "GatedLinearAttention", "GatedLinearAttentionSpec", "DifferentialAttention", "DifferentialAttentionSpec",
+    "StreamsBlock", "StreamsBlockSpec", "StreamsRMSNorm", "StreamsRMSNormSpec", "StreamsWrite", "StreamsWriteSpec",
 ]

@@ -31,7 +31,16 @@ Further options of the spec, all off by default:
 * ``gate``: the heads' outputs are multiplied by ``sigmoid(Wg h)`` before the output projection,
   ``element`` by element (``Wg`` has as many rows as the concatenated heads) or ``head`` by head
   (one row per head); ``Wg`` reads the same ``h`` and its rows follow v's in the fused matrix;
-* ``o_bias``: whether the output projection has a bias (None: as ``bias`` says).
+* ``o_bias``: whether the output projection has a bias (None: as ``bias`` says);
+* ``qk_norm_scope="row"``: the q/k norm runs over all of a token's query rows at once (and over
+  all of its key rows), with weights of that size, instead of head by head;
+* ``sinks``: a learned number per query head whose exponential joins the softmax's denominator
+  without a key or a value.
+
+A position encoding whose tables cover fewer dims than the head size rotates the first of each
+head's dims (pairs ``(i, i + rotated/2)``) and passes the rest. That, and the norm over whole rows,
+are served by the kernel set's ``qkv_norm_rope_write``, which also fills a head up to the kernels'
+head size itself (the projection's rows are then left as they are).
 """
 
 from __future__ import annotations
@@ -64,6 +73,8 @@ class AttentionSpec:
     keep_first: int = 0
     gate: str = "none"  # "element", "head"
     o_bias: bool | None = None  # None: as bias
+    qk_norm_scope: str = "head"  # "row": one norm over all query rows of a token, one over all key rows
+    sinks: bool = False
     kind: str = "attention"
 
 
@@ -87,10 +98,21 @@ class PagedAttention(Mixer):
         self.v_size = 0 if spec.values_are_keys else spec.num_kv_heads * self.value_dim
         self.gate_size = {"none": 0, "element": spec.num_heads * self.value_dim, "head": spec.num_heads}[spec.gate]
         self.o_bias_on = spec.bias if spec.o_bias is None else spec.o_bias
+        if spec.qk_norm_scope not in ("head", "row"):
+            raise ValueError(f"attention: qk_norm_scope {spec.qk_norm_scope!r} is not known")
+        self.rot_dims = 2 * self.rotary[0].shape[1] if self.rotary is not None else 0
+        if self.rot_dims > spec.head_dim:
+            raise ValueError("attention: more rotated dims than the head size")
+        # whole-row norms and partly rotated heads go through the kernel that prepares a token's rows at once
+        self.by_rows = ((spec.qk_norm_scope == "row" and spec.qk_norm_eps is not None)
+                        or (self.rotary is not None and self.rot_dims != spec.head_dim))
+        if self.by_rows and (spec.bias or spec.gate == "element" or spec.keep_first):
+            raise NotImplementedError("attention: whole-row norm or a partly rotated head with bias, element gate or kept keys")
         # the plain path (fused projection, rotation, cache write and attention) serves none of these
         self.extended = (spec.qk_norm_eps is not None or spec.values_are_keys or spec.head_temperature
                          or spec.distance_slopes is not None or spec.chunk > 0
-                         or self.value_dim != spec.head_dim or spec.keep_first > 0 or spec.gate != "none")
+                         or self.value_dim != spec.head_dim or spec.keep_first > 0 or spec.gate != "none"
+                         or spec.sinks or self.by_rows)
         # The attention kernels take head sizes that are multiples of 16. With the score options on,
         # any other head size is padded with zeros up to the next one when the weights are bound:
         # zero dims change no dot product, the norm divides by the true size, and the padded dims
@@ -98,7 +120,7 @@ class PagedAttention(Mixer):
         widest = max(spec.head_dim, self.value_dim)
         self.kernel_dim = widest + ((-widest) % 16 if self.extended else 0)
         self.pad = self.kernel_dim - spec.head_dim  # of a query or key head; a value head's may differ
-        if self.pad and self.rotary is not None:
+        if self.pad and self.rotary is not None and not self.by_rows:
             raise NotImplementedError("a padded head size with rotary positions")
         self.slopes = None
         if spec.distance_slopes is not None:
@@ -119,8 +141,11 @@ class PagedAttention(Mixer):
         if self.o_bias_on:
             decls["o.bias"] = ParamDecl((s.hidden_size,), "bias")
         if s.qk_norm_eps is not None and s.qk_norm_weight:
-            decls["q_norm.weight"] = ParamDecl((s.head_dim,), "scale")
-            decls["k_norm.weight"] = ParamDecl((s.head_dim,), "scale")
+            row = s.qk_norm_scope == "row"
+            decls["q_norm.weight"] = ParamDecl((self.q_size if row else s.head_dim,), "scale")
+            decls["k_norm.weight"] = ParamDecl((self.kv_size if row else s.head_dim,), "scale")
+        if s.sinks:
+            decls["sinks"] = ParamDecl((s.num_heads,), "scale")
         if s.head_temperature:
             decls["temperature"] = ParamDecl((s.num_heads,), "scale")
         return decls
@@ -133,9 +158,18 @@ class PagedAttention(Mixer):
         self.q_norm_weight = params.get("q_norm.weight")
         self.k_norm_weight = params.get("k_norm.weight")
         self.temperature = params.get("temperature")
+        self.sinks = params.get("sinks")
         s = self.spec
         if s.qk_norm_eps is not None and not s.qk_norm_weight:  # the kernel's norm multiplies by a weight: ones
-            self.q_norm_weight = self.k_norm_weight = torch.ones(s.head_dim, dtype=torch.float32, device=self.env.device)
+            row = s.qk_norm_scope == "row"
+            self.q_norm_weight = torch.ones(self.q_size if row else s.head_dim, dtype=torch.float32, device=self.env.device)
+            self.k_norm_weight = torch.ones(self.kv_size if row else s.head_dim, dtype=torch.float32, device=self.env.device)
+        if self.by_rows:  # the kernel fills the heads up; only the output projection meets the padded heads
+            if self.kernel_dim != self.value_dim:
+                o = self.o_weight.new_zeros(s.hidden_size, s.num_heads, self.kernel_dim)
+                o[:, :, :self.value_dim] = self.o_weight.view(s.hidden_size, s.num_heads, self.value_dim)
+                self.o_weight = o.view(s.hidden_size, s.num_heads * self.kernel_dim).contiguous()
+            return
         if self.gate_size and self.qkv_bias is not None:  # the gate has no bias
             self.qkv_bias = torch.cat([self.qkv_bias, self.qkv_bias.new_zeros(self.gate_size)])
         if self.kernel_dim != s.head_dim or self.kernel_dim != self.value_dim:
@@ -234,6 +268,8 @@ class PagedAttention(Mixer):
         score options: three launches, and one more with an output gate."""
         s, ops = self.spec, self.ops
         qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=torch.float32)
+        if self.by_rows:
+            return self._by_rows(qkv, step, cache, tables, cos, sin)
         q = ops.norm_rope_kv_write(
             qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim,
             norm_dim=s.head_dim,
@@ -246,8 +282,32 @@ class PagedAttention(Mixer):
             q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim, scale=s.scale,
             window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
             page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
-            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk, keep_first=s.keep_first)
+            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk, keep_first=s.keep_first,
+            sinks=self.sinks)
         if s.gate != "none":  # the gate's columns follow v's in the projection's rows
             col0 = (s.num_heads + s.num_kv_heads * (1 if s.values_are_keys else 2)) * self.kernel_dim
             ops.sigmoid_gate_mul(o, qkv, col0, 1 if s.gate == "element" else self.kernel_dim)
+        return o
+
+    def _by_rows(self, qkv, step, cache, tables, cos, sin):
+        """The same three or four launches with the kernel that prepares all rows of a token."""
+        s, ops = self.spec, self.ops
+        normed = s.qk_norm_eps is not None
+        q = ops.qkv_norm_rope_write(
+            qkv, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
+            num_value_heads=0 if s.values_are_keys else s.num_kv_heads, head_dim=s.head_dim,
+            value_dim=self.value_dim, out_dim=self.kernel_dim,
+            q_weight=self.q_norm_weight if normed else None, k_weight=self.k_norm_weight if normed else None,
+            eps=s.qk_norm_eps or 0.0, norm_rows=s.qk_norm_scope == "row",
+            positions=step.positions, token_seq=step.token_seq, cos=cos, sin=sin,
+            k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,
+            block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)
+        o = ops.paged_attention(
+            q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=self.kernel_dim, scale=s.scale,
+            window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
+            page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
+            head_scale=self.temperature, slopes=self.slopes, chunk=s.chunk, sinks=self.sinks)
+        if s.gate == "head":  # one gate column per head, behind q, k (and v)
+            col0 = self.q_size + self.kv_size + self.v_size
+            ops.sigmoid_gate_mul(o, qkv, col0, self.kernel_dim)
         return o

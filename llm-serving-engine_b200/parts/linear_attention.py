@@ -1,4 +1,5 @@
-"""Linear attention with a fixed decay per head: a recurrence over a matrix state, no softmax.
+"""Linear attention: a recurrence over a matrix state, no softmax; with a fixed decay per head
+(``decay_linear_attention``) or a decay per key channel made from the token (``gated_linear_attention``, below).
 
 Per head, with ``q_t, k_t`` of ``key_dim`` values and ``v_t`` of ``value_dim``:
 
@@ -105,4 +106,81 @@ class DecayLinearAttention(Mixer):
             group=s.value_dim if s.out_norm == "heads" else self.vg,
             weight=self.norm_weight, eps=s.eps, gate_activation=s.gate_activation,
             out_dtype=self.env.dtype)
+        return project_into(ops, y, self.o_weight, None, self.env.residual_dtype, None, may_defer)
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention whose decay is made from the token itself, one number per key channel:
+
+        alpha_t = sigmoid(z_t)^(1/tau),  z_t = A2 (A1 h_t) + b         (heads x key_dim values, float32)
+        S_t = diag(alpha_t) S_{t-1} + k_t v_t^T,   o_t = S_t^T (query_scale * q_t)
+
+    Each head's ``o`` is divided by its root mean square and multiplied by a weight of ``value_dim``
+    values that all heads share; the concatenated heads are multiplied by ``silu(h Wg^T)`` (or
+    its sigmoid) and projected by ``Wo``. ``decay_rank`` is the inner size of the two decay
+    matrices."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    eps: float
+    query_scale: float = 1.0
+    gate_activation: str = "silu"
+    kind: str = "gated_linear_attention"
+
+
+@MIXERS.register("gated_linear_attention")
+class GatedLinearAttention(Mixer):
+    keeps_running_state = True
+
+    def __init__(self, spec: GatedLinearAttentionSpec, env) -> None:
+        super().__init__(spec, env)
+        if spec.gate_activation not in ("silu", "sigmoid"):
+            raise ValueError("unknown activation")
+        if spec.decay_rank < 1 or spec.tau <= 0:
+            raise ValueError("gated linear attention: decay_rank and tau must be positive")
+        self.qk = spec.num_heads * spec.key_dim
+        self.vg = spec.num_heads * spec.value_dim
+
+    def param_decls(self):
+        s = self.spec
+        return {
+            "qkvg.weight": ParamDecl((2 * self.qk + 2 * self.vg, s.hidden_size), "matrix"),
+            "decay_in.weight": ParamDecl((s.decay_rank, s.hidden_size), "matrix"),
+            "decay_out.weight": ParamDecl((self.qk, s.decay_rank), "matrix"),
+            "decay_out.bias": ParamDecl((self.qk,), "bias"),
+            "norm.weight": ParamDecl((s.value_dim,), "scale"),
+            "o.weight": ParamDecl((s.hidden_size, self.vg), "matrix"),
+        }
+
+    def bind(self, params):
+        self.qkvg_weight = params["qkvg.weight"]
+        self.decay_in_weight = params["decay_in.weight"]
+        self.decay_out_weight = params["decay_out.weight"]
+        self.decay_out_bias = params["decay_out.bias"]
+        self.norm_weight = params["norm.weight"].repeat(self.spec.num_heads).contiguous()  # the same for every head
+        self.o_weight = params["o.weight"]
+
+    def cache_need(self):
+        s = self.spec
+        return StateNeed((s.num_heads, s.value_dim, s.key_dim), torch.float32)
+
+    accepts_deferral = True
+
+    def forward(self, h, step, cache, may_defer=False):
+        s, ops = self.spec, self.ops
+        proj = ops.linear(h, self.qkvg_weight, None, out_dtype=torch.float32)
+        low = ops.linear(h, self.decay_in_weight, None, out_dtype=self.env.dtype)
+        z = ops.linear(low, self.decay_out_weight, self.decay_out_bias, out_dtype=torch.float32)
+        o = ops.decay_linear_attention(
+            proj, num_heads=s.num_heads, key_dim=s.key_dim, value_dim=s.value_dim, decay=None,
+            state=cache.state, step=step, activation="none", key_scale=1.0, cos=None, sin=None,
+            decay_logits=z, decay_root=s.tau, query_scale=s.query_scale)
+        y = ops.gated_group_norm(
+            o, proj, gate_offset=2 * self.qk + self.vg, group=s.value_dim, weight=self.norm_weight,
+            eps=s.eps, gate_activation=s.gate_activation, out_dtype=self.env.dtype)
         return project_into(ops, y, self.o_weight, None, self.env.residual_dtype, None, may_defer)

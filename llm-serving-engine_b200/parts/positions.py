@@ -6,6 +6,15 @@ are built once in float64 and stored in float32, as the reference does
 angles are never rounded to 16 bits. Frequency scaling ``linear`` and ``llama3`` follow
 src/llmserve/models/layers.py:24-58.
 
+Frequency scaling ``yarn``: with ``d(t) = dims * ln(original / (2 pi t)) / (2 ln theta)``, ``lo =
+max(floor(d(yarn_fast)), 0)``, ``hi = min(ceil(d(yarn_slow)), dims - 1)`` and ``ramp_i = clamp((i -
+lo) / max(hi - lo, 0.001), 0, 1)``, frequency i becomes ``f_i / factor * ramp_i + f_i * (1 -
+ramp_i)`` (fast-turning pairs keep their frequency, slow ones are stretched by ``factor``), and
+both tables are multiplied by ``0.1 ln(factor) + 1``.
+
+``head_dim`` is the number of rotated dims: a mixer whose heads are larger rotates the first
+``head_dim`` dims of each head (pairs ``(i, i + head_dim/2)``) and passes the rest.
+
 ``none``: no position information (for mixers that carry order in their own state).
 
 ``sinusoid``: an absolute encoding added to the embedded tokens: entry 2i of the vector of
@@ -33,7 +42,14 @@ class RotarySpec:
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     original_max_positions: int = 0
+    yarn_fast: float = 32.0  # turns over the original length above which a pair keeps its frequency
+    yarn_slow: float = 1.0  # turns below which a pair is stretched by the whole factor
     kind: str = "rope"
+
+
+def rotary_table_factor(spec: RotarySpec) -> float:
+    """What cos and sin are multiplied by (one, except under ``yarn``)."""
+    return 0.1 * math.log(spec.factor) + 1.0 if spec.scaling_type == "yarn" else 1.0
 
 
 @dataclass(frozen=True)
@@ -59,6 +75,14 @@ def rotary_inverse_frequencies(spec: RotarySpec) -> torch.Tensor:
         mid = (1 - smooth) * scaled / spec.factor + smooth * scaled
         is_mid = (wavelen >= high_wavelen) & (wavelen <= low_wavelen)
         inv = torch.where(is_mid, mid, scaled)
+    elif spec.scaling_type == "yarn":
+        def pair_of(turns: float) -> float:
+            return d * math.log(spec.original_max_positions / (2.0 * math.pi * turns)) / (2.0 * math.log(spec.theta))
+
+        lo = max(math.floor(pair_of(spec.yarn_fast)), 0)
+        hi = min(math.ceil(pair_of(spec.yarn_slow)), d - 1)
+        ramp = ((torch.arange(d // 2, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        inv = inv / spec.factor * ramp + inv * (1.0 - ramp)
     elif spec.scaling_type != "default":
         raise NotImplementedError(f"rope scaling {spec.scaling_type!r}")
     return inv
@@ -72,8 +96,9 @@ class RotaryPositionEncoding(PositionEncoding):
             raise ValueError(f"rotary positions need an even head size, got {spec.head_dim}")
         inv = rotary_inverse_frequencies(spec)
         ang = torch.outer(torch.arange(env.max_positions, dtype=torch.float64), inv)
-        self.cos = ang.cos().float().contiguous().to(env.device)
-        self.sin = ang.sin().float().contiguous().to(env.device)
+        mag = rotary_table_factor(spec)
+        self.cos = (ang.cos() * mag).float().contiguous().to(env.device)
+        self.sin = (ang.sin() * mag).float().contiguous().to(env.device)
 
     def rotary_tables(self):
         return self.cos, self.sin

@@ -352,10 +352,11 @@ class PlainOps:
         return x.to(out_dtype)
 
     def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
-                               activation, key_scale, cos, sin):
+                               activation, key_scale, cos, sin, decay_logits=None, decay_root=1.0,
+                               query_scale=1.0):
         T, H, dk, dv = proj.shape[0], num_heads, key_dim, value_dim
         p = proj.float()
-        q = p[:, : H * dk].view(T, H, dk)
+        q = p[:, : H * dk].view(T, H, dk) * query_scale
         k = p[:, H * dk : 2 * H * dk].view(T, H, dk)
         v = p[:, 2 * H * dk : 2 * H * dk + H * dv].view(T, H, dv)
         if activation == "silu":
@@ -373,6 +374,12 @@ class PlainOps:
             a, b = cu[s_], cu[s_ + 1]
             S = state[slots[s_]].clone() if ctx[s_] - (b - a) > 0 else torch.zeros_like(state[0])  # [H, dv, dk]
             for t in range(a, b):
+                if decay_logits is not None:  # a decay per key channel and token: sigmoid(z)^(1/root)
+                    z = decay_logits[t].float().view(H, dk)
+                    alpha = torch.exp(torch.nn.functional.logsigmoid(z) / decay_root)
+                    S = alpha[:, None, :] * S + v[t][:, :, None] * k[t][:, None, :]
+                    out[t] = torch.einsum("hvk,hk->hv", S, q[t])
+                    continue
                 S = decay[:, None, None] * S + v[t][:, :, None] * k[t][:, None, :]
                 out[t] = torch.einsum("hvk,hk->hv", S, q[t])
             state[slots[s_]] = S
@@ -387,6 +394,74 @@ class PlainOps:
             y = y * weight
         gate = g / (1 + torch.exp(-g)) if gate_activation == "silu" else 1 / (1 + torch.exp(-g))
         return (y * gate).to(out_dtype)
+
+    # ------------------------------------------------------------------ residual streams
+    def streams_spread(self, x, streams, scale=1.0):
+        return (x.float() * scale).repeat(1, streams)
+
+    def streams_read_norm(self, x, read, weight, eps, streams, out_dtype, rows=None):
+        T, W = x.shape[0], x.shape[1] // streams
+        xs = x.view(T, streams, W)
+        if rows is not None:
+            xs = xs[rows.long()]
+        u = torch.einsum("s,tsw->tw", read.float(), xs)
+        return (u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+    def streams_write(self, x, y, scale, mix, out, streams, then_read=None, then_weight=None, then_eps=0.0,
+                      out_dtype=None):
+        T, W = x.shape[0], x.shape[1] // streams
+        y = y.resolve() if hasattr(y, "resolve") else y
+        y = y.float() * scale if scale is not None else y.float()
+        xs = x.view(T, streams, W)
+        xs.copy_(torch.einsum("sr,tsw->trw", mix.float(), xs) + out.float()[None, :, None] * y[:, None, :])
+        if then_read is None:
+            return None
+        return self.streams_read_norm(x, then_read, then_weight, then_eps, streams, out_dtype)
+
+    # ------------------------------------------------------------------ rows of q, k, v prepared a token at a time
+    def qkv_norm_rope_write(self, qkv, *, num_heads, num_kv_heads, num_value_heads, head_dim, value_dim, out_dim,
+                            q_weight, k_weight, eps, norm_rows, positions, token_seq, cos, sin, k_pages,
+                            v_pages, block_tables, page_tokens, out_dtype, temp_coef=0.0, temp_every=0):
+        T, D, Dv, Dp = qkv.shape[0], head_dim, value_dim, out_dim
+        nq, nk, nv = num_heads, num_kv_heads, num_value_heads
+        p = qkv.float()
+        q, k = p[:, : nq * D], p[:, nq * D : (nq + nk) * D]
+        v = k.reshape(T, nk, D) if nv == 0 else p[:, (nq + nk) * D : (nq + nk) * D + nv * Dv].reshape(T, nv, Dv)
+        if q_weight is not None:
+            if norm_rows:
+                q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+                k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
+            else:
+                q = (q.reshape(T, nq, D) * torch.rsqrt(q.reshape(T, nq, D).pow(2).mean(-1, keepdim=True) + eps) * q_weight).reshape(T, -1)
+                k = (k.reshape(T, nk, D) * torch.rsqrt(k.reshape(T, nk, D).pow(2).mean(-1, keepdim=True) + eps) * k_weight).reshape(T, -1)
+        pos = positions.long()
+        if temp_every:
+            q = q * (1.0 + temp_coef * torch.log(torch.floor((pos.float() + 1.0) / temp_every) + 1.0))[:, None]
+        q, k = q.reshape(T, nq, D), k.reshape(T, nk, D)
+        if cos is not None:
+            half = cos.shape[1]
+            c, s_ = cos[pos][:, None, :], sin[pos][:, None, :]
+            rot = lambda x: torch.cat([x[..., :half] * c - x[..., half : 2 * half] * s_,
+                                       x[..., half : 2 * half] * c + x[..., :half] * s_, x[..., 2 * half :]], -1)
+            q, k = rot(q), rot(k)
+        if nv:
+            v = v.repeat_interleave(nk // nv, dim=1)
+        fill = lambda x: torch.nn.functional.pad(x, (0, Dp - x.shape[-1]))
+        if k_pages is not None:
+            page = block_tables[token_seq.long(), pos // page_tokens].long()
+            off = pos % page_tokens
+            k_pages[page, :, off] = fill(k).to(k_pages.dtype)
+            v_pages[page, :, off] = fill(v).to(v_pages.dtype)
+        return fill(q).to(out_dtype).reshape(T, nq * Dp).contiguous()
+
+    def differential_combine(self, a, proj, *, gate_col0, num_heads, group, head_dim, value_dim, lam, eps,
+                             out_scale, out_dtype):
+        T, H, n = a.shape[0], num_heads, group
+        maps = a.float().view(T, H // n, 2, n, head_dim)[..., :value_dim]  # (key group, map, head in group)
+        o = (maps[:, :, 0] - lam * maps[:, :, 1]).reshape(T, H, value_dim)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+        g = torch.sigmoid(proj[:, gate_col0 : gate_col0 + H].float())
+        return (o * g[:, :, None]).reshape(T, H * value_dim).to(out_dtype)
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):
