@@ -758,14 +758,22 @@ void norm_rope_kv_write(const Tensor& qkv, Tensor& q_out, int64_t nq, int64_t nk
        "norm_rope_kv_write");
 }
 
-void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, const Tensor& decay, const Tensor& cu_q,
+void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, const OptTensor& decay, const Tensor& cu_q,
                             const Tensor& ctx_lens, const Tensor& slots, int64_t H, int64_t dk, int64_t dv,
                             const OptTensor& cos, const OptTensor& sin, bool silu, double key_scale,
-                            int64_t max_chunks, const OptTensor& chunks) {
+                            int64_t max_chunks, const OptTensor& chunks, const OptTensor& gate_z,
+                            double decay_root, double query_scale) {
   check_f32(proj, "proj");
   check_f32(out, "out");
   check_state(state, "state", dk);
-  check_f32(decay, "decay");
+  TORCH_CHECK(decay.has_value() != gate_z.has_value(),
+              "decay_linear_attention: give the decays per head or the logits of decays per channel and token");
+  if (decay) check_f32(*decay, "decay");
+  if (gate_z) {
+    check_f32(*gate_z, "gate_z");
+    TORCH_CHECK(gate_z->dim() == 2 && gate_z->size(0) == proj.size(0) && gate_z->size(1) >= H * dk && decay_root > 0,
+                "decay_linear_attention: the decay logits must be [T, >= heads * key_dim] and the root positive");
+  }
   check_i32(cu_q, "cu_q");
   check_i32(ctx_lens, "ctx_lens");
   check_i32(slots, "slots");
@@ -774,7 +782,7 @@ void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, cons
               "decay_linear_attention: out must be [T, heads * value_dim]");
   TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == dv && state.size(3) == dk,
               "decay_linear_attention: state must be [slots, heads, value_dim, key_dim]");
-  TORCH_CHECK(decay.numel() == H && cu_q.numel() == ctx_lens.numel() + 1 && slots.numel() >= ctx_lens.numel(),
+  TORCH_CHECK((!decay || decay->numel() == H) && cu_q.numel() == ctx_lens.numel() + 1 && slots.numel() >= ctx_lens.numel(),
               "decay_linear_attention: per-head or per-sequence arrays disagree");
   TORCH_CHECK(dk > 0 && dk <= 256 && dv > 0, "decay_linear_attention: key size must be at most 256");
   TORCH_CHECK(cos.has_value() == sin.has_value(), "decay_linear_attention: cos and sin go together");
@@ -786,21 +794,25 @@ void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, cons
                 "decay_linear_attention: cos and sin must be [positions, rotated dims / 2]");
     rot = 2 * (int)cos->size(1);
   }
-  float* chunk_ptr = nullptr;
+  float *chunk_ptr = nullptr, *chunk_decay = nullptr;
   if (max_chunks > 1) {
     TORCH_CHECK(chunks.has_value(), "decay_linear_attention: chunked portions need the scratch");
     check_f32(*chunks, "chunks");
     // every sequence of more than one chunk holds at most tokens / chunk + 1 of them
     const int64_t L = lse_linear_attention_chunk();
     const int64_t most = proj.size(0) / L + ctx_lens.numel();
-    TORCH_CHECK(chunks->numel() >= most * H * dv * dk, "decay_linear_attention: the scratch is too small");
+    TORCH_CHECK(chunks->numel() >= most * H * (dv * dk + (gate_z ? dk : 0)),
+                "decay_linear_attention: the scratch is too small");
     chunk_ptr = chunks->data_ptr<float>();
+    if (gate_z) chunk_decay = chunk_ptr + most * H * dv * dk;  // behind the chunks' states
   }
   done(lse_decay_linear_attention(proj.data_ptr<float>(), proj.size(1), out.data_ptr<float>(), state.data_ptr<float>(),
-                                  decay.data_ptr<float>(), cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                                  decay ? decay->data_ptr<float>() : nullptr, cu_q.data_ptr<int>(), ctx_lens.data_ptr<int>(),
                                   slots.data_ptr<int>(), (int)ctx_lens.numel(), (int)H, (int)dk, (int)dv,
                                   cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, rot,
-                                  silu ? 1 : 0, (float)key_scale, (int)max_chunks, chunk_ptr, stream()),
+                                  silu ? 1 : 0, (float)key_scale, (int)max_chunks, chunk_ptr, stream(),
+                                  gate_z ? gate_z->data_ptr<float>() : nullptr, gate_z ? gate_z->size(1) : 0,
+                                  (float)decay_root, (float)query_scale, chunk_decay),
        "decay_linear_attention");
 }
 
@@ -1096,6 +1108,129 @@ void act_rows(const Tensor& in, Tensor& out, int64_t act) {
        "act_rows");
 }
 
+// ------------------------------------------------------------------ residual streams, rows of q/k/v, differential attention
+void streams_spread(const Tensor& x, Tensor& out, int64_t S, double scale) {
+  check_f32(x, "x");
+  check_f32(out, "out");
+  TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && S > 0 && out.size(0) == x.size(0) && out.size(1) == S * x.size(1),
+              "streams_spread: out must be [T, streams * width]");
+  done(lse_streams_spread(x.data_ptr<float>(), out.data_ptr<float>(), (int)x.size(0), (int)x.size(1), (int)S,
+                          (float)scale, stream()),
+       "streams_spread");
+}
+
+void streams_read_norm(const Tensor& x, const Tensor& read, const Tensor& w, double eps, Tensor& out, int64_t S,
+                       const OptTensor& rows) {
+  check_f32(x, "x");
+  check_f32(read, "read");
+  check_f32(w, "weight");
+  check_cuda(out, "out");
+  TORCH_CHECK(x.dim() == 2 && S > 0 && x.size(1) % S == 0 && read.numel() == S, "streams_read_norm: x must be [T, streams * width]");
+  const int64_t W = x.size(1) / S;
+  const int* rp = nullptr;
+  int64_t n = x.size(0);
+  if (rows) {
+    check_i32(*rows, "rows");
+    rp = rows->data_ptr<int>();
+    n = rows->numel();
+  }
+  TORCH_CHECK(w.numel() == W && out.dim() == 2 && out.size(0) == n && out.size(1) == W, "streams_read_norm: out must be [rows, width]");
+  done(lse_streams_read_norm(x.data_ptr<float>(), read.data_ptr<float>(), w.data_ptr<float>(), (float)eps,
+                             out.data_ptr(), out_code(out, "out"), rp, (int)n, (int)W, (int)S, stream()),
+       "streams_read_norm");
+}
+
+void streams_write(Tensor& x, const Tensor& y, const OptTensor& scale, const Tensor& mix, const Tensor& outw,
+                   int64_t S, const OptTensor& then_read, const OptTensor& then_w, double then_eps,
+                   const OptTensor& out) {
+  check_f32(x, "x");
+  check_cuda(y, "y");
+  check_f32(mix, "mix");
+  check_f32(outw, "out weights");
+  TORCH_CHECK(x.dim() == 2 && S > 0 && x.size(1) % S == 0 && mix.numel() == S * S && outw.numel() == S,
+              "streams_write: x must be [T, streams * width], mix [streams, streams]");
+  const int64_t W = x.size(1) / S;
+  TORCH_CHECK(y.dim() == 2 && y.size(0) == x.size(0) && y.size(1) == W, "streams_write: y must be [T, width]");
+  TORCH_CHECK(then_read.has_value() == then_w.has_value() && then_read.has_value() == out.has_value(),
+              "streams_write: the read that follows needs its weights, the norm's weight and an output");
+  void* op = nullptr;
+  int ocode = LSE_F32;
+  if (out) {
+    check_cuda(*out, "out");
+    TORCH_CHECK(out->dim() == 2 && out->size(0) == x.size(0) && out->size(1) == W, "streams_write: out must be [T, width]");
+    op = out->data_ptr();
+    ocode = out_code(*out, "out");
+  }
+  done(lse_streams_write(x.data_ptr<float>(), y.data_ptr(), dtype_code(y, "y"), opt_f32(scale, W, "scale"),
+                         mix.data_ptr<float>(), outw.data_ptr<float>(), (int)x.size(0), (int)W, (int)S,
+                         opt_f32(then_read, S, "then_read"), opt_f32(then_w, W, "then_weight"), (float)then_eps, op,
+                         ocode, stream()),
+       "streams_write");
+}
+
+void qkv_norm_rope_write(const Tensor& proj, Tensor& q_out, int64_t nq, int64_t nk, int64_t nv, int64_t D, int64_t Dv,
+                         int64_t Dp, const OptTensor& qw, const OptTensor& kw, double eps, double temp_coef,
+                         int64_t temp_every, const Tensor& positions, const Tensor& token_seq, const OptTensor& cos,
+                         const OptTensor& sin, const OptTensor& k_pages, const OptTensor& v_pages,
+                         const Tensor& block_tables, int64_t page_tokens) {
+  check_f32(proj, "proj");
+  check_cuda(q_out, "q_out");
+  check_i32(positions, "positions");
+  check_i32(token_seq, "token_seq");
+  check_i32(block_tables, "block_tables");
+  const int64_t T = proj.size(0);
+  TORCH_CHECK(proj.dim() == 2 && nq > 0 && nk > 0 && nv >= 0 && D > 0 && Dp >= D && Dp <= 256 &&
+                  proj.size(1) >= (nq + nk) * D + nv * Dv,
+              "qkv_norm_rope_write: the projection is too narrow for these heads");
+  TORCH_CHECK(q_out.dim() == 2 && q_out.size(0) == T && q_out.size(1) == nq * Dp, "qkv_norm_rope_write: q_out shape");
+  TORCH_CHECK(positions.numel() >= T && token_seq.numel() >= T && block_tables.dim() == 2,
+              "qkv_norm_rope_write: the batch arrays disagree");
+  TORCH_CHECK(qw.has_value() == kw.has_value() && cos.has_value() == sin.has_value() &&
+                  k_pages.has_value() == v_pages.has_value(),
+              "qkv_norm_rope_write: weights, tables and pages come in pairs");
+  int rot = 0;
+  if (cos) {
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 2 && sin->sizes() == cos->sizes() && 2 * cos->size(1) <= D,
+                "qkv_norm_rope_write: cos and sin must be [positions, rotated dims / 2]");
+    rot = 2 * (int)cos->size(1);
+  }
+  void *kp = nullptr, *vp = nullptr;
+  if (k_pages) {
+    check_cuda(*k_pages, "k_pages");
+    check_cuda(*v_pages, "v_pages");
+    TORCH_CHECK(k_pages->scalar_type() == q_out.scalar_type() && v_pages->scalar_type() == q_out.scalar_type() &&
+                    k_pages->dim() == 4 && k_pages->size(1) == nk && k_pages->size(2) == page_tokens &&
+                    k_pages->size(3) == Dp && v_pages->sizes() == k_pages->sizes(),
+                "qkv_norm_rope_write: pages must be [pages, key heads, page_tokens, out_dim] of q_out's dtype");
+    kp = k_pages->data_ptr();
+    vp = v_pages->data_ptr();
+  }
+  done(lse_qkv_norm_rope_write(proj.data_ptr<float>(), proj.size(1), (int)T, (int)nq, (int)nk, (int)nv, (int)D, (int)Dv,
+                               (int)Dp, opt_f32(qw, nq * D, "q weight"), opt_f32(kw, nk * D, "k weight"), (float)eps,
+                               (float)temp_coef, (int)temp_every, positions.data_ptr<int>(), token_seq.data_ptr<int>(),
+                               cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, rot,
+                               q_out.data_ptr(), kp, vp, out_code(q_out, "q_out"), block_tables.data_ptr<int>(),
+                               (int)block_tables.size(1), (int)page_tokens, stream()),
+       "qkv_norm_rope_write");
+}
+
+void differential_combine(const Tensor& a, const Tensor& gate, int64_t gate_col0, int64_t H, int64_t n, int64_t Dp,
+                          int64_t Dv, double lam, double eps, double out_scale, Tensor& out) {
+  check_cuda(a, "a");
+  check_f32(gate, "gate");
+  check_cuda(out, "out");
+  TORCH_CHECK(a.dim() == 2 && a.size(1) == 2 * H * Dp && gate.dim() == 2 && gate.size(0) == a.size(0) &&
+                  gate_col0 >= 0 && gate_col0 + H <= gate.size(1) && out.dim() == 2 && out.size(0) == a.size(0) &&
+                  out.size(1) == H * Dv && out.scalar_type() == a.scalar_type(),
+              "differential_combine: need a [T, 2*heads*head_dim], gate columns inside gate, out [T, heads*value_dim] of a's dtype");
+  done(lse_differential_combine(a.data_ptr(), out_code(a, "a"), gate.data_ptr<float>() + gate_col0, gate.size(1),
+                                (int)a.size(0), (int)H, (int)n, (int)Dp, (int)Dv, (float)lam, (float)eps,
+                                (float)out_scale, out.data_ptr(), out_code(out, "out"), stream()),
+       "differential_combine");
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding);
   m.def("add_rmsnorm", &add_rmsnorm);
@@ -1140,7 +1275,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mix_normed", &mix_normed);
   m.def("gated_group_norm", &gated_group_norm);
   m.def("norm_rope_kv_write", &norm_rope_kv_write);
-  m.def("decay_linear_attention", &decay_linear_attention);
+  m.def("decay_linear_attention", &decay_linear_attention, py::arg("proj"), py::arg("out"), py::arg("state"),
+        py::arg("decay"), py::arg("cu_q"), py::arg("ctx_lens"), py::arg("slots"), py::arg("H"), py::arg("dk"),
+        py::arg("dv"), py::arg("cos"), py::arg("sin"), py::arg("silu"), py::arg("key_scale"), py::arg("max_chunks"),
+        py::arg("chunks"), py::arg("gate_z") = py::none(), py::arg("decay_root") = 1.0, py::arg("query_scale") = 1.0);
+  m.def("streams_spread", &streams_spread);
+  m.def("streams_read_norm", &streams_read_norm);
+  m.def("streams_write", &streams_write);
+  m.def("qkv_norm_rope_write", &qkv_norm_rope_write);
+  m.def("differential_combine", &differential_combine);
   m.def("linear_attention_chunk", []() { return (int64_t)lse_linear_attention_chunk(); });
   m.def("paged_attention_from_sums", &paged_attention_from_sums);
   m.def("attention_takes_sums", &attention_takes_sums);

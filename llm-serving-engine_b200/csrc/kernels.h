@@ -168,7 +168,50 @@ int lse_decay_linear_attention(const float* proj, long long stride, float* out, 
                                const float* decay, const int* cu_q, const int* ctx_lens,
                                const int* slots, int num_seqs, int H, int dk, int dv,
                                const float* cos, const float* sin, int rot, int silu,
-                               float key_scale, int max_chunks, float* chunks, cudaStream_t stream);
+                               float key_scale, int max_chunks, float* chunks, cudaStream_t stream,
+                               // a decay per key channel and token, alpha = sigmoid(z)^(1/decay_root),
+                               // z = gate_z[t, h*dk + i] (decay may then be null); q is multiplied by
+                               // query_scale; chunk_decay: scratch of (chunks as above) * H * dk floats
+                               const float* gate_z = nullptr, long long gate_stride = 0, float decay_root = 1.f,
+                               float query_scale = 1.f, float* chunk_decay = nullptr);
+// ---- several residual streams, rows of q/k/v prepared a token at a time, differential attention
+// (streams_mixers.cu). The residual state is float32 [T, S * W]: a token's S streams of W values.
+
+// out[t, s*W + i] = x[t, i] * scale for every stream s.
+int lse_streams_spread(const float* x, float* out, int T, int W, int S, float scale, cudaStream_t stream);
+
+// out[r] = u / rms(u) * w with u = sum_s read[s] * x[t, s], t = rows ? rows[r] : r. S <= 8.
+int lse_streams_read_norm(const float* x, const float* read, const float* w, float eps, void* out,
+                          int out_dtype, const int* rows, int n_rows, int W, int S, cudaStream_t stream);
+
+// x[t, r] <- sum_s mix[s*S + r] * x[t, s] + outw[r] * scale * y[t] for all r at once (scale [W] or
+// null). y: LSE_F32, LSE_BF16, or LSE_FIXED64 sums (taken: left zero; W a multiple of 4). With
+// then_read: also out[t] = u / rms(u) * then_w, u = sum_r then_read[r] * (new) x[t, r].
+int lse_streams_write(float* x, const void* y, int y_dtype, const float* scale, const float* mix,
+                      const float* outw, int T, int W, int S, const float* then_read, const float* then_w,
+                      float then_eps, void* out, int out_dtype, cudaStream_t stream);
+
+// proj float32 [T, stride]: nq query heads of D, nk key heads of D, then nv value heads of Dv
+// (nv == 0: a key head's value is the key as projected; otherwise nk is a multiple of nv and value
+// head g goes to the pages of key heads g*nk/nv ..). With qw/kw ([nq*D], [nk*D]): q and k divided
+// by the root mean square of all their values of the token and multiplied by the weights. With
+// temp_every > 0: q *= 1 + temp_coef * ln((pos + 1) / temp_every + 1) (integer division). With
+// cos/sin [positions, rot/2]: the first rot dims of every q and k head turned, dim i paired with
+// i + rot/2. q goes to q_out [T, nq*Dp], k and v into pages [pages, nk, page_tokens, Dp] of
+// `dtype` (or both null when the layer only reads); dims from D (Dv) up to Dp are zero.
+int lse_qkv_norm_rope_write(const float* proj, long long stride, int T, int nq, int nk, int nv, int D, int Dv,
+                            int Dp, const float* qw, const float* kw, float eps, float temp_coef,
+                            int temp_every, const int* positions, const int* token_seq, const float* cos,
+                            const float* sin, int rot, void* q_out, void* k_pages, void* v_pages, int dtype,
+                            const int* block_tables, int table_stride, int page_tokens, cudaStream_t stream);
+
+// a [T, 2H*Dp]: for every key group of n heads, the heads' first attention maps, then their second
+// ones. out[t, h] (Dv values) = o / rms(o) * out_scale * sigmoid(gate[t*gate_stride + h]),
+// o = a1 - lam * a2 over the first Dv dims. a and out have the same dtype. Dv <= 256.
+int lse_differential_combine(const void* a, int a_dtype, const float* gate, long long gate_stride, int T,
+                             int H, int n, int Dp, int Dv, float lam, float eps, float out_scale, void* out,
+                             int out_dtype, cudaStream_t stream);
+
 // ---- table-sum embeddings, latent attention, routed experts (latent_moe.cu)
 
 // x[t] += table[row], row = (previous token * mul_prev + token * mul_cur) mod buckets, or row

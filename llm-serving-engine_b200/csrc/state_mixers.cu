@@ -411,7 +411,18 @@ struct LinAttnArgs {
   int P, CB;              // lanes per column; columns per block
   int L;                  // chunk length
   int phase;              // 0: launch A, 2: launch C
+  // a decay per key channel and token instead of decay[h]: alpha = sigmoid(z)^inv_root
+  const float* gate_z;    // [T, gate_stride], heads x dk logits per row; null: the fixed decays
+  long long gate_stride;
+  float inv_root;
+  float query_scale;      // q is multiplied by this
+  float* chunk_decay;     // scratch [chunks of all chunked sequences, H, dk]: the product of a chunk's alphas
 };
+
+__device__ __forceinline__ float root_of_sigmoid(float z, float inv_root) {
+  // log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
+  return expf(-(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * inv_root);
+}
 
 // Index of a sequence's first chunk in the scratch: only sequences of more than one chunk have any.
 __device__ __forceinline__ int chunk_base(const int* cu_q, int seq, int L) {
@@ -433,7 +444,10 @@ __device__ __forceinline__ void la_copy(float* smem, const float* gmem, bool wid
 // this one is computed: two buffers); activation, rotation and the key's scale are then applied
 // in place. Row i of a token's q (or k) lies at (i / RPT) * (RPT + PAD) + i % RPT: the pad keeps
 // the 16-byte reads of the P lanes of a column on different banks.
-template <int P>
+// GATED: the decay of row i at token t is alpha_t[i] (its logits are staged like q and k and turned
+// into alphas in place); launch A also leaves the product of each chunk's alphas for launch B, and
+// launch C carries the running product of the chunk's alphas per row instead of a power of the decay.
+template <int P, bool GATED>
 __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
   extern __shared__ __align__(16) float la_smem[];
   pdl_trigger();
@@ -455,21 +469,23 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   const int p = threadIdx.x % P, jl = 2 * (threadIdx.x / P);
   const int j = cb * CB + jl;  // this thread's columns: j and j + 1
   constexpr int ldq = P * (LA_RPT + LA_PAD);
-  constexpr int per_buf = 2 * LA_TT * ldq + LA_TT * CB;  // q [TT][ldq], k [TT][ldq], v [TT][CB]
-  const float decay = a.decay[h];
+  // q [TT][ldq], k [TT][ldq], v [TT][CB], and with GATED the alphas [TT][ldq]
+  constexpr int per_buf = (GATED ? 3 : 2) * LA_TT * ldq + LA_TT * CB;
+  const float decay = GATED ? 1.f : a.decay[h];
   float S[LA_RPT], S1[LA_RPT];
   const bool has0 = j < dv, has1 = j + 1 < dv;
   const size_t column = ((size_t)h * dv + (has0 ? j : 0)) * dk + p * LA_RPT;
   const size_t per_state = (size_t)H * dv * dk;
   float* st = a.state + (size_t)a.slots[seq] * per_state + column;
   float* chunk_states = nullptr;
-  if (num_chunks > 1) chunk_states = a.chunks + (size_t)chunk_base(a.cu_q, seq, L) * per_state + column;
+  const int first_chunk = num_chunks > 1 ? chunk_base(a.cu_q, seq, L) : 0;
+  if (num_chunks > 1) chunk_states = a.chunks + (size_t)first_chunk * per_state + column;
   // rows beyond key_dim and columns beyond value_dim stay zero in both buffers (nothing else is
   // ever read that the copies below do not write)
   const int cols = min(CB, dv - cb * CB);  // value columns of this block
   if (dk != P * LA_RPT || cols != CB)
     for (int i = threadIdx.x; i < 2 * per_buf; i += LA_THREADS) la_smem[i] = 0.f;
-  const bool wide_qk = (dk % 4 == 0) && (a.stride % 4 == 0);
+  const bool wide_qk = (dk % 4 == 0) && (a.stride % 4 == 0) && (!GATED || a.gate_stride % 4 == 0);
   const bool wide_v = wide_qk && (dv % 4 == 0) && (CB % 4 == 0);
   const int qk_step = wide_qk ? 4 : 1, v_step = wide_v ? 4 : 1;
   const int qk_units = dk / qk_step, v_units = (cols + v_step - 1) / v_step;  // cols % 4 == 0 when wide
@@ -486,6 +502,8 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
       const int at = tt * ldq + (i / LA_RPT) * (LA_RPT + LA_PAD) + (i % LA_RPT);
       la_copy(qs + at, row, wide_qk);
       if (!add_pass) la_copy(ks + at, row + (size_t)H * dk, wide_qk);
+      if constexpr (GATED)
+        la_copy(vs + LA_TT * CB + at, a.gate_z + (size_t)(r0 + t0 + tt) * a.gate_stride + (size_t)h * dk + i, wide_qk);
     }
     if (!add_pass)
       for (int idx = threadIdx.x; idx < tn * v_units; idx += LA_THREADS) {
@@ -519,6 +537,10 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   const int half = a.rot / 2;
   const int work = dk - half;  // a rotated pair is one piece of work, every other row one
   float carried = 1.f;  // launch C: decay^(tokens of the chunk so far)
+  float run[GATED ? LA_RPT : 1];  // GATED: the product of the chunk's alphas so far, row by row
+#pragma unroll
+  for (int r = 0; r < (GATED ? LA_RPT : 1); ++r) run[r] = 1.f;
+  const bool keeps_run = GATED && (add_pass || (num_chunks > 1 && cb == 0 && threadIdx.x < P));
   int buf = 0;
   for (int t0 = t_begin; t0 < t_end; t0 += LA_TT, buf ^= 1) {
     const int tn = min(LA_TT, t_end - t0);
@@ -532,7 +554,8 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     float* qs = la_smem + buf * per_buf;
     float* ks = qs + LA_TT * ldq;
     float* vs = ks + LA_TT * ldq;
-    if (a.silu || a.rot || a.key_scale != 1.f) {
+    float* gs = vs + LA_TT * CB;
+    if (a.silu || a.rot || a.key_scale != 1.f || a.query_scale != 1.f || GATED) {
       for (int idx = threadIdx.x; idx < tn * work; idx += LA_THREADS) {
         const int tt = idx / work, w = idx - tt * work;
         const int i = w < half ? w : w + half;  // rows [half, rot) are done with their partners
@@ -552,14 +575,16 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
           }
           const size_t tab = (size_t)(pos0 + t0 + tt) * half + i;
           const float cs = a.cos[tab], sn = a.sin[tab];
-          qs[atp] = qp * cs + q * sn;
+          qs[atp] = (qp * cs + q * sn) * a.query_scale;
           ks[atp] = (kp * cs + k * sn) * a.key_scale;
+          if constexpr (GATED) gs[atp] = root_of_sigmoid(gs[atp], a.inv_root);
           const float q2 = q * cs - qp * sn, k2 = k * cs - kp * sn;
           q = q2;
           k = k2;
         }
-        qs[at] = q;
+        qs[at] = q * a.query_scale;
         ks[at] = k * a.key_scale;
+        if constexpr (GATED) gs[at] = root_of_sigmoid(gs[at], a.inv_root);
       }
       if (a.silu && !add_pass)
         for (int idx = threadIdx.x; idx < tn * cols; idx += LA_THREADS) {
@@ -570,6 +595,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     }
     const float4* q4 = reinterpret_cast<const float4*>(qs + p * (LA_RPT + LA_PAD));
     const float4* k4 = reinterpret_cast<const float4*>(ks + p * (LA_RPT + LA_PAD));
+    const float4* g4 = reinterpret_cast<const float4*>(gs + p * (LA_RPT + LA_PAD));
     const float* vcol = vs + jl;
     // after the reduction lane p == 0 holds column j's sum and lane p == 1 column j + 1's
     const int mine = P > 1 ? (p & 1) : 0;
@@ -577,7 +603,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     const size_t out_stride = (size_t)H * dv;
     const bool writes = P > 1 ? (p < 2 && j + mine < dv) : has0;
 #pragma unroll 2
-    for (int tt = 0; tt < tn; ++tt, q4 += ldq / 4, k4 += ldq / 4, vcol += CB, dst += out_stride) {
+    for (int tt = 0; tt < tn; ++tt, q4 += ldq / 4, k4 += ldq / 4, g4 += ldq / 4, vcol += CB, dst += out_stride) {
       float acc0 = 0.f, acc1 = 0.f;
       if (!add_pass) {
         const float2 vj = *reinterpret_cast<const float2*>(vcol);
@@ -585,10 +611,19 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4], k = k4[r4];
           const float qv[4] = {q.x, q.y, q.z, q.w}, kv[4] = {k.x, k.y, k.z, k.w};
+          float gv[4] = {decay, decay, decay, decay};
+          if constexpr (GATED) {
+            const float4 g = g4[r4];
+            gv[0] = g.x; gv[1] = g.y; gv[2] = g.z; gv[3] = g.w;
+            if (keeps_run) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) run[4 * r4 + e] *= gv[e];
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            S[4 * r4 + e] = fmaf(decay, S[4 * r4 + e], kv[e] * vj.x);
-            S1[4 * r4 + e] = fmaf(decay, S1[4 * r4 + e], kv[e] * vj.y);
+            S[4 * r4 + e] = fmaf(gv[e], S[4 * r4 + e], kv[e] * vj.x);
+            S1[4 * r4 + e] = fmaf(gv[e], S1[4 * r4 + e], kv[e] * vj.y);
             acc0 = fmaf(S[4 * r4 + e], qv[e], acc0);
             acc1 = fmaf(S1[4 * r4 + e], qv[e], acc1);
           }
@@ -597,7 +632,16 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
 #pragma unroll
         for (int r4 = 0; r4 < LA_RPT / 4; ++r4) {
           const float4 q = q4[r4];
-          const float qv[4] = {q.x, q.y, q.z, q.w};
+          float qv[4] = {q.x, q.y, q.z, q.w};
+          if constexpr (GATED) {  // what is left of the state before the chunk, row by row
+            const float4 g = g4[r4];
+            const float gv[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              run[4 * r4 + e] *= gv[e];
+              qv[e] *= run[4 * r4 + e];
+            }
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             acc0 = fmaf(S[4 * r4 + e], qv[e], acc0);
@@ -628,6 +672,14 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
     __syncthreads();  // the buffer is free for the tile after the next
   }
   if (add_pass) return;
+  if constexpr (GATED) {
+    if (keeps_run) {  // the first P threads of the head's first slice hold every row once
+      float* dst = a.chunk_decay + ((size_t)(first_chunk + c) * H + h) * dk + p * LA_RPT;
+#pragma unroll
+      for (int r = 0; r < LA_RPT; ++r)
+        if (p * LA_RPT + r < dk) dst[r] = run[r];
+    }
+  }
   float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
   auto store_column = [&](const float (&src)[LA_RPT], float* dst) {
     if (dk % 4 == 0) {
@@ -649,7 +701,8 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
 // Launch B: one thread per element of the state and sequence of more than one chunk.
 __global__ void chain_chunk_states_kernel(float* __restrict__ chunks, float* __restrict__ state,
                                           const float* __restrict__ decay, const int* __restrict__ cu_q,
-                                          const int* __restrict__ slots, int H, int dv, int dk, int L) {
+                                          const int* __restrict__ slots, int H, int dv, int dk, int L,
+                                          const float* chunk_decay) {
   pdl_trigger();
   const int seq = blockIdx.y;
   const int n = cu_q[seq + 1] - cu_q[seq];
@@ -660,21 +713,28 @@ __global__ void chain_chunk_states_kernel(float* __restrict__ chunks, float* __r
     pdl_wait();  // as above
     return;
   }
-  float* mine = chunks + (size_t)chunk_base(cu_q, seq, L) * per_state + e;
-  const float d = decay[e / ((size_t)dv * dk)];
+  const int first_chunk = chunk_base(cu_q, seq, L);
+  float* mine = chunks + (size_t)first_chunk * per_state + e;
+  const int head = (int)(e / ((size_t)dv * dk));
+  const float d = chunk_decay ? 1.f : decay[head];
   const float whole = powf(d, (float)L);
+  // with a decay per channel and token: the product of chunk c's alphas of this element's row
+  const float* across = chunk_decay ? chunk_decay + ((size_t)first_chunk * H + head) * dk + e % dk : nullptr;
   pdl_wait();
   float S = mine[0];
   for (int c0 = 1; c0 < num_chunks; c0 += 8) {  // a round's loads are all in flight before its chain
-    float E[8];
+    float E[8], A[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) E[u] = c0 + u < num_chunks ? __ldcg(mine + (size_t)(c0 + u) * per_state) : 0.f;
+    for (int u = 0; u < 8; ++u) {
+      E[u] = c0 + u < num_chunks ? __ldcg(mine + (size_t)(c0 + u) * per_state) : 0.f;
+      A[u] = (across && c0 + u < num_chunks) ? __ldcg(across + (size_t)(c0 + u) * H * dk) : 0.f;
+    }
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int c = c0 + u;
       if (c < num_chunks) {
         const int len = min(L, n - c * L);
-        S = fmaf(len == L ? whole : powf(d, (float)len), S, E[u]);
+        S = fmaf(across ? A[u] : (len == L ? whole : powf(d, (float)len)), S, E[u]);
         mine[(size_t)c * per_state] = S;
       }
     }
@@ -815,8 +875,12 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
                                           const int* slots, int num_seqs, int H, int dk, int dv,
                                           const float* cos, const float* sin, int rot, int silu,
                                           float key_scale, int max_chunks, float* chunks,
-                                          cudaStream_t stream) {
+                                          cudaStream_t stream, const float* gate_z, long long gate_stride,
+                                          float decay_root, float query_scale, float* chunk_decay) {
   if (num_seqs <= 0) return LSE_OK;
+  if ((!gate_z && !decay) || (gate_z && (decay_root <= 0.f || gate_stride < (long long)H * dk)) ||
+      (gate_z && max_chunks > 1 && !chunk_decay))
+    return LSE_BAD_ARGUMENT;
   if (H <= 0 || dk <= 0 || dv <= 0 || dk > 256 || rot < 0 || rot > dk || rot % 2 || (rot && (!cos || !sin)) ||
       num_seqs > 65535 || max_chunks < 1 || max_chunks > 65535 || (max_chunks > 1 && !chunks))
     return LSE_BAD_ARGUMENT;
@@ -824,29 +888,41 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
   a.proj = proj; a.stride = stride; a.out = out; a.state = state; a.chunks = chunks; a.decay = decay;
   a.cu_q = cu_q; a.ctx_lens = ctx_lens; a.slots = slots; a.cos = cos; a.sin = sin; a.H = H; a.dk = dk;
   a.dv = dv; a.rot = rot; a.silu = silu; a.key_scale = key_scale;
+  a.gate_z = gate_z; a.gate_stride = gate_stride; a.inv_root = gate_z ? 1.f / decay_root : 1.f;
+  a.query_scale = query_scale; a.chunk_decay = chunk_decay;
+  const bool gated = gate_z != nullptr;
   a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
   a.CB = 2 * LA_THREADS / a.P;
-  void (*kernel)(LinAttnArgs) = a.P == 1 ? decay_linear_attention_kernel<1>
-                                : a.P == 2 ? decay_linear_attention_kernel<2>
-                                : a.P == 4 ? decay_linear_attention_kernel<4>
-                                : a.P == 8 ? decay_linear_attention_kernel<8>
-                                : a.P == 16 ? decay_linear_attention_kernel<16>
-                                            : decay_linear_attention_kernel<32>;
+  void (*kernel)(LinAttnArgs) =
+      gated ? (a.P == 1 ? decay_linear_attention_kernel<1, true>
+               : a.P == 2 ? decay_linear_attention_kernel<2, true>
+               : a.P == 4 ? decay_linear_attention_kernel<4, true>
+               : a.P == 8 ? decay_linear_attention_kernel<8, true>
+               : a.P == 16 ? decay_linear_attention_kernel<16, true>
+                           : decay_linear_attention_kernel<32, true>)
+            : (a.P == 1 ? decay_linear_attention_kernel<1, false>
+               : a.P == 2 ? decay_linear_attention_kernel<2, false>
+               : a.P == 4 ? decay_linear_attention_kernel<4, false>
+               : a.P == 8 ? decay_linear_attention_kernel<8, false>
+               : a.P == 16 ? decay_linear_attention_kernel<16, false>
+                           : decay_linear_attention_kernel<32, false>);
   a.L = lse_linear_attention_chunk();
   a.phase = 0;
   const int slices = (dv + a.CB - 1) / a.CB;
-  const size_t smem = 2 * ((size_t)2 * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
-  static bool configured[33] = {};
-  if (!configured[a.P]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess)
+  const size_t smem =
+      2 * ((size_t)(gated ? 3 : 2) * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
+  static bool configured[2][33] = {};
+  if (!configured[gated][a.P]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (gated ? 160 : 112) * 1024) !=
+        cudaSuccess)
       return LSE_LAUNCH_FAILED;
-    configured[a.P] = true;
+    configured[gated][a.P] = true;
   }
   launch(kernel, dim3(H * slices, max_chunks, num_seqs), LA_THREADS, smem, stream, a);
   if (max_chunks > 1) {
     const size_t per_state = (size_t)H * dv * dk;
     launch(chain_chunk_states_kernel, dim3((unsigned)((per_state + 255) / 256), num_seqs), 256, 0, stream,
-           chunks, state, decay, cu_q, slots, H, dv, dk, a.L);
+           chunks, state, decay, cu_q, slots, H, dv, dk, a.L, (const float*)(gated ? chunk_decay : nullptr));
     a.phase = 2;
     launch(kernel, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
   }

@@ -1,0 +1,427 @@
+// Kernels of blocks that carry several residual streams, of attention whose queries and keys are
+// prepared a whole token at a time, and of differential attention.
+//
+//   streams_spread        every stream of a token starts as its embedded row times a constant
+//   streams_read_norm     u = sum_s read[s] x_s, then u / rms(u) * w, per token (or per listed row)
+//   streams_write         x_t <- sum_s mix[s, t] x_s + out[t] * scale * y for all streams t of a
+//                         token at once; optionally followed, while the block holds the token's
+//                         streams, by the read and norm that the next sublayer needs
+//   qkv_norm_rope_write   per token: RMS norm over all query rows (and over all key rows) with
+//                         weights of that size, a query factor that grows with the position, the
+//                         first `rot` dims of each head turned, heads filled up with zeros to the
+//                         attention kernels' head size, keys and values written into their pages
+//                         (each value head into the pages of `repeat` key heads)
+//   differential_combine  o = a1 - lam * a2 of a head's two attention maps, divided by its root
+//                         mean square, scaled and gated by a sigmoid per head
+//
+// The streams, the sums, the norms, the angles and the gates are float32 arithmetic whatever the
+// types of the tensors are; values are rounded once when they are stored in the compute dtype.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lse {
+
+#define LSE_CHECK_LAUNCH() (cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
+
+constexpr int SM_MAX_STREAMS = 8;
+constexpr int SM_THREADS = 256;
+
+// ------------------------------------------------------------------------------------ spread
+__global__ void streams_spread_kernel(const float* __restrict__ x, float* __restrict__ out, int W, int S,
+                                      float scale, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / W;
+  const int c = (int)(i - t * W);
+  const float v = x[i] * scale;
+  float* dst = out + t * (long long)S * W + c;
+  for (int s = 0; s < S; ++s) dst[(size_t)s * W] = v;
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void ld_vec(const T* p, float (&v)[V]) {
+  if constexpr (V == 4) load4<T>(p, v);
+  else v[0] = Num<T>::to_float(p[0]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void st_vec(T* p, const float (&v)[V]) {
+  if constexpr (V == 4) store4<T>(p, v);
+  else p[0] = Num<T>::from_float(v[0]);
+}
+
+// ------------------------------------------------------------------------------------ read + norm
+// One block per output row; u is kept in shared memory between the two visits.
+template <typename TO, int V>
+__global__ void __launch_bounds__(SM_THREADS)
+streams_read_norm_kernel(const float* __restrict__ x, const float* __restrict__ read,
+                         const float* __restrict__ w, float eps, TO* __restrict__ out,
+                         const int* __restrict__ rows, int W, int S) {
+  extern __shared__ __align__(16) float u_row[];  // [W]
+  __shared__ float scratch[32];
+  __shared__ float rd[SM_MAX_STREAMS];
+  pdl_trigger();
+  if (threadIdx.x < S) rd[threadIdx.x] = read[threadIdx.x];
+  __syncthreads();
+  pdl_wait();
+  const size_t t = rows ? (size_t)rows[blockIdx.x] : (size_t)blockIdx.x;
+  const float* xr = x + t * (size_t)S * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < W; i += SM_THREADS * V) {
+    float u[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) u[j] = 0.f;
+    for (int s = 0; s < S; ++s) {
+      float xv[V];
+      ld_vec<float, V>(xr + (size_t)s * W + i, xv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) u[j] = fmaf(rd[s], xv[j], u[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      ss += u[j] * u[j];
+      u_row[i + j] = u[j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)W + eps);
+  TO* o = out + (size_t)blockIdx.x * W;
+  for (int i = threadIdx.x * V; i < W; i += SM_THREADS * V) {
+    float u[V], wv[V];
+    ld_vec<float, V>(u_row + i, u);  // this thread's own writes
+    ld_vec<float, V>(w + i, wv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) u[j] *= inv * wv[j];
+    st_vec<TO, V>(o + i, u);
+  }
+}
+
+// ------------------------------------------------------------------------------------ write (+ read + norm)
+// One block per token. TY: the sublayer's result as float32, bfloat16, or the fixed-point sums of
+// a few-rows product (taken: zeros are left behind).
+template <typename TY, typename TO, int V>
+__global__ void __launch_bounds__(SM_THREADS)
+streams_write_kernel(float* __restrict__ x, const TY* y, const float* __restrict__ scale,
+                     const float* __restrict__ mix, const float* __restrict__ outw, int W, int S,
+                     const float* __restrict__ then_read, const float* __restrict__ then_w, float then_eps,
+                     TO* __restrict__ out) {
+  extern __shared__ __align__(16) float u_row[];  // [W], only with then_read
+  __shared__ float scratch[32];
+  __shared__ float m[SM_MAX_STREAMS * SM_MAX_STREAMS], ow[SM_MAX_STREAMS], rd[SM_MAX_STREAMS];
+  pdl_trigger();
+  if (threadIdx.x < S * S) m[threadIdx.x] = mix[threadIdx.x];
+  if (threadIdx.x < S) {
+    ow[threadIdx.x] = outw[threadIdx.x];
+    rd[threadIdx.x] = then_read ? then_read[threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  pdl_wait();
+  const size_t t = blockIdx.x;
+  float* xr = x + t * (size_t)S * W;
+  const TY* yr = y + t * (size_t)W;
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < W; i += SM_THREADS * V) {
+    float xs[SM_MAX_STREAMS][V], yv[V];
+#pragma unroll
+    for (int s = 0; s < SM_MAX_STREAMS; ++s)
+      if (s < S) ld_vec<float, V>(xr + (size_t)s * W + i, xs[s]);
+    ld_vec<TY, V>(yr + i, yv);
+    if (scale) {
+      float sv[V];
+      ld_vec<float, V>(scale + i, sv);
+#pragma unroll
+      for (int j = 0; j < V; ++j) yv[j] *= sv[j];
+    }
+    float u[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) u[j] = 0.f;
+#pragma unroll
+    for (int r = 0; r < SM_MAX_STREAMS; ++r) {
+      if (r < S) {
+        float nv[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) nv[j] = ow[r] * yv[j];
+#pragma unroll
+        for (int s = 0; s < SM_MAX_STREAMS; ++s)
+          if (s < S) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) nv[j] = fmaf(m[s * S + r], xs[s][j], nv[j]);
+          }
+        st_vec<float, V>(xr + (size_t)r * W + i, nv);
+#pragma unroll
+        for (int j = 0; j < V; ++j) u[j] = fmaf(rd[r], nv[j], u[j]);
+      }
+    }
+    if (then_read) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        ss += u[j] * u[j];
+        u_row[i + j] = u[j];
+      }
+    }
+  }
+  if (!then_read) return;
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)W + then_eps);
+  TO* o = out + t * (size_t)W;
+  for (int i = threadIdx.x * V; i < W; i += SM_THREADS * V) {
+    float u[V], wv[V];
+    ld_vec<float, V>(u_row + i, u);
+    ld_vec<float, V>(then_w + i, wv);
+#pragma unroll
+    for (int j = 0; j < V; ++j) u[j] *= inv * wv[j];
+    st_vec<TO, V>(o + i, u);
+  }
+}
+
+// ------------------------------------------------------------------------------------ q, k, v of a token
+struct QkvRowsArgs {
+  const float* proj;  // [T, stride]: q heads (nq x D), k heads (nk x D), then nv value heads of Dv
+  long long stride;
+  int nq, nk, nv;     // nv == 0: a key head's value is the key as projected
+  int D, Dv, Dp;      // sizes in the projection, and of a head in q_out and in the pages
+  const float* qw;    // [nq * D], [nk * D] or both null
+  const float* kw;
+  float eps;
+  float temp_coef;    // q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1), if temp_every > 0
+  int temp_every;
+  const int* positions;
+  const int* token_seq;
+  const float* cos;   // [positions, rot / 2] or null
+  const float* sin;
+  int rot;
+  void* q_out;        // [T, nq * Dp]
+  void* k_pages;      // [pages, nk, page_tokens, Dp], or both null
+  void* v_pages;
+  const int* block_tables;
+  int table_stride, page_tokens;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(SM_THREADS) qkv_norm_rope_write_kernel(const QkvRowsArgs a) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = a.positions[t];
+  const int D = a.D, Dp = a.Dp, nq = a.nq, nk = a.nk;
+  size_t page_row = 0;  // of key head 0 of this token, in units of Dp
+  if (a.k_pages) {
+    const int pi = pos / a.page_tokens, off = pos - pi * a.page_tokens;
+    const int page = a.block_tables[(size_t)a.token_seq[t] * a.table_stride + pi];
+    page_row = (size_t)page * nk * a.page_tokens + off;
+  }
+  pdl_wait();
+  const float* row = a.proj + (size_t)t * a.stride;
+  float inv_q = 1.f, inv_k = 1.f;
+  if (a.qw) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq * D; i += SM_THREADS) sq += row[i] * row[i];
+    for (int i = threadIdx.x; i < nk * D; i += SM_THREADS) sk += row[nq * D + i] * row[nq * D + i];
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    inv_q = rsqrtf(sq / (float)(nq * D) + a.eps);
+    inv_k = rsqrtf(sk / (float)(nk * D) + a.eps);
+  }
+  if (a.temp_every > 0)
+    inv_q *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+  const int half = a.rot / 2;
+  const float* cr = a.cos ? a.cos + (size_t)pos * half : nullptr;
+  const float* sr = a.cos ? a.sin + (size_t)pos * half : nullptr;
+  T* q_out = (T*)a.q_out + (size_t)t * nq * Dp;
+  T* k_pages = (T*)a.k_pages;
+  T* v_pages = (T*)a.v_pages;
+  const int heads = a.k_pages ? nq + nk : nq;
+  for (int idx = threadIdx.x; idx < heads * Dp; idx += SM_THREADS) {
+    const int h = idx / Dp, i = idx - h * Dp;
+    const bool is_q = h < nq;
+    float v = 0.f;
+    if (i < D) {
+      const float* src = row + (size_t)h * D;  // the key heads follow the query heads
+      const float* w = a.qw ? (is_q ? a.qw + (size_t)h * D : a.kw + (size_t)(h - nq) * D) : nullptr;
+      const float inv = is_q ? inv_q : inv_k;
+      v = src[i] * inv * (w ? w[i] : 1.f);
+      if (i < a.rot) {
+        const int ip = i < half ? i + half : i - half;
+        const float vp = src[ip] * inv * (w ? w[ip] : 1.f);
+        const int f = i < half ? i : i - half;
+        v = i < half ? v * cr[f] - vp * sr[f] : v * cr[f] + vp * sr[f];
+      }
+    }
+    if (is_q) q_out[idx] = Num<T>::from_float(v);
+    else k_pages[(page_row + (size_t)(h - nq) * a.page_tokens) * Dp + i] = Num<T>::from_float(v);
+  }
+  if (!a.v_pages) return;
+  const int repeat = a.nv > 0 ? nk / a.nv : 1;
+  for (int idx = threadIdx.x; idx < nk * Dp; idx += SM_THREADS) {
+    const int h = idx / Dp, i = idx - h * Dp;
+    float v = 0.f;
+    if (a.nv == 0) {
+      if (i < D) v = row[(size_t)(nq + h) * D + i];
+    } else if (i < a.Dv) {
+      v = row[(size_t)(nq + nk) * D + (size_t)(h / repeat) * a.Dv + i];
+    }
+    v_pages[(page_row + (size_t)h * a.page_tokens) * Dp + i] = Num<T>::from_float(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------ differential combine
+// One warp per (token, head). a [T, 2H * Dp] holds, for key group g (n heads each), the n heads'
+// first maps and then their second maps; out [T, H * Dv].
+constexpr int DC_WARPS = 4;
+template <typename TA, typename TO>
+__global__ void differential_combine_kernel(const TA* __restrict__ a, const float* __restrict__ gate,
+                                            long long gate_stride, int H, int n, int Dp, int Dv, float lam,
+                                            float eps, float out_scale, TO* __restrict__ out, int T) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long th = (long long)blockIdx.x * DC_WARPS + warp;
+  if (th >= (long long)T * H) return;
+  const int t = (int)(th / H), h = (int)(th - (long long)t * H);
+  const int g = h / n, r = h - g * n;
+  const TA* a1 = a + ((size_t)t * 2 * H + (size_t)(2 * g) * n + r) * Dp;
+  const TA* a2 = a1 + (size_t)n * Dp;
+  float o[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int i = lane + 32 * c;
+    o[c] = i < Dv ? Num<TA>::to_float(a1[i]) - lam * Num<TA>::to_float(a2[i]) : 0.f;
+    ss += o[c] * o[c];
+  }
+  ss = warp_sum(ss);
+  const float z = gate[(size_t)t * gate_stride + h];
+  const float f = rsqrtf(ss / (float)Dv + eps) * out_scale / (1.f + expf(-z));
+  TO* dst = out + ((size_t)t * H + h) * Dv;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int i = lane + 32 * c;
+    if (i < Dv) dst[i] = Num<TO>::from_float(o[c] * f);
+  }
+}
+
+}  // namespace lse
+
+using namespace lse;
+
+extern "C" int lse_streams_spread(const float* x, float* out, int T, int W, int S, float scale,
+                                  cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (W <= 0 || S <= 0) return LSE_BAD_ARGUMENT;
+  const long long n = (long long)T * W;
+  launch(streams_spread_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, out, W, S, scale, n);
+  return LSE_CHECK_LAUNCH();
+}
+
+// Rows of up to this many floats are kept in shared memory between a block's two visits.
+static const int kStreamsMaxWidth = 48 * 1024;
+
+template <typename K>
+static int allow_row(K kernel, size_t bytes) {
+  if (bytes <= 48 * 1024) return LSE_OK;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024) == cudaSuccess
+             ? LSE_OK
+             : LSE_LAUNCH_FAILED;
+}
+
+extern "C" int lse_streams_read_norm(const float* x, const float* read, const float* w, float eps, void* out,
+                                     int out_dtype, const int* rows, int n_rows, int W, int S,
+                                     cudaStream_t stream) {
+  if (n_rows <= 0) return LSE_OK;
+  if (W <= 0 || W > kStreamsMaxWidth || S <= 0 || S > SM_MAX_STREAMS) return LSE_BAD_ARGUMENT;
+  const size_t smem = (size_t)W * sizeof(float);
+  const bool wide = W % 4 == 0;
+#define LSE_RN(TO, V)                                                                                   \
+  do {                                                                                                  \
+    if (allow_row(streams_read_norm_kernel<TO, V>, smem) != LSE_OK) return LSE_LAUNCH_FAILED;           \
+    launch(streams_read_norm_kernel<TO, V>, n_rows, SM_THREADS, smem, stream, x, read, w, eps, (TO*)out, \
+           rows, W, S);                                                                                 \
+  } while (0)
+  if (out_dtype == LSE_BF16) {
+    if (wide) LSE_RN(bf16, 4); else LSE_RN(bf16, 1);
+  } else if (out_dtype == LSE_F32) {
+    if (wide) LSE_RN(float, 4); else LSE_RN(float, 1);
+  } else {
+    return LSE_BAD_ARGUMENT;
+  }
+#undef LSE_RN
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_streams_write(float* x, const void* y, int y_dtype, const float* scale, const float* mix,
+                                 const float* outw, int T, int W, int S, const float* then_read,
+                                 const float* then_w, float then_eps, void* out, int out_dtype,
+                                 cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (W <= 0 || W > kStreamsMaxWidth || S <= 0 || S > SM_MAX_STREAMS || (then_read && (!then_w || !out)))
+    return LSE_BAD_ARGUMENT;
+  const bool wide = W % 4 == 0;
+  if (y_dtype == LSE_FIXED64 && !wide) return LSE_BAD_ARGUMENT;
+  const size_t smem = then_read ? (size_t)W * sizeof(float) : 0;
+  if (!then_read) out_dtype = LSE_F32;
+#define LSE_SW(TY, TO, V)                                                                                  \
+  do {                                                                                                     \
+    if (allow_row(streams_write_kernel<TY, TO, V>, smem) != LSE_OK) return LSE_LAUNCH_FAILED;              \
+    launch(streams_write_kernel<TY, TO, V>, T, SM_THREADS, smem, stream, x, (const TY*)y, scale, mix, outw, \
+           W, S, then_read, then_w, then_eps, (TO*)out);                                                   \
+  } while (0)
+#define LSE_SW_OUT(TY, V)                              \
+  do {                                                 \
+    if (out_dtype == LSE_BF16) LSE_SW(TY, bf16, V);    \
+    else if (out_dtype == LSE_F32) LSE_SW(TY, float, V); \
+    else return LSE_BAD_ARGUMENT;                      \
+  } while (0)
+  if (y_dtype == LSE_F32) {
+    if (wide) LSE_SW_OUT(float, 4); else LSE_SW_OUT(float, 1);
+  } else if (y_dtype == LSE_BF16) {
+    if (wide) LSE_SW_OUT(bf16, 4); else LSE_SW_OUT(bf16, 1);
+  } else if (y_dtype == LSE_FIXED64) {
+    LSE_SW_OUT(fixed64, 4);
+  } else {
+    return LSE_BAD_ARGUMENT;
+  }
+#undef LSE_SW_OUT
+#undef LSE_SW
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_qkv_norm_rope_write(const float* proj, long long stride, int T, int nq, int nk, int nv,
+                                       int D, int Dv, int Dp, const float* qw, const float* kw, float eps,
+                                       float temp_coef, int temp_every, const int* positions,
+                                       const int* token_seq, const float* cos, const float* sin, int rot,
+                                       void* q_out, void* k_pages, void* v_pages, int dtype,
+                                       const int* block_tables, int table_stride, int page_tokens,
+                                       cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (nq <= 0 || nk <= 0 || nv < 0 || (nv > 0 && nk % nv) || D <= 0 || Dp < D || (nv > 0 && (Dv <= 0 || Dp < Dv)) ||
+      (!qw != !kw) || (!cos != !sin) || (!k_pages != !v_pages) || rot < 0 || rot > D || rot % 2 || (rot && !cos) ||
+      page_tokens <= 0 || temp_every < 0 || stride < (long long)(nq + nk) * D + (long long)nv * Dv)
+    return LSE_BAD_ARGUMENT;
+  QkvRowsArgs a;
+  a.proj = proj; a.stride = stride; a.nq = nq; a.nk = nk; a.nv = nv; a.D = D; a.Dv = Dv; a.Dp = Dp;
+  a.qw = qw; a.kw = kw; a.eps = eps; a.temp_coef = temp_coef; a.temp_every = temp_every;
+  a.positions = positions; a.token_seq = token_seq; a.cos = cos; a.sin = sin; a.rot = cos ? rot : 0;
+  a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.block_tables = block_tables;
+  a.table_stride = table_stride; a.page_tokens = page_tokens;
+  if (dtype == LSE_BF16) launch(qkv_norm_rope_write_kernel<bf16>, T, SM_THREADS, 0, stream, a);
+  else if (dtype == LSE_F32) launch(qkv_norm_rope_write_kernel<float>, T, SM_THREADS, 0, stream, a);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_differential_combine(const void* a, int a_dtype, const float* gate, long long gate_stride,
+                                        int T, int H, int n, int Dp, int Dv, float lam, float eps,
+                                        float out_scale, void* out, int out_dtype, cudaStream_t stream) {
+  if (T <= 0) return LSE_OK;
+  if (H <= 0 || n <= 0 || H % n || Dv <= 0 || Dv > 256 || Dp < Dv || a_dtype != out_dtype) return LSE_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)(((long long)T * H + DC_WARPS - 1) / DC_WARPS);
+  if (a_dtype == LSE_BF16)
+    launch(differential_combine_kernel<bf16, bf16>, blocks, DC_WARPS * 32, 0, stream, (const bf16*)a, gate,
+           gate_stride, H, n, Dp, Dv, lam, eps, out_scale, (bf16*)out, T);
+  else if (a_dtype == LSE_F32)
+    launch(differential_combine_kernel<float, float>, blocks, DC_WARPS * 32, 0, stream, (const float*)a, gate,
+           gate_stride, H, n, Dp, Dv, lam, eps, out_scale, (float*)out, T);
+  else return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}

@@ -27,7 +27,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr"]
-CORE_CU = ["pointwise.cu", "gemm_f32.cu", "gemm_bf16_tc.cu", "sampling.cu", "state_mixers.cu", "latent_moe.cu", "grouped_gemm_tc.cu", "rotary_latent.cu"]
+CORE_CU = ["pointwise.cu", "gemm_f32.cu", "gemm_bf16_tc.cu", "sampling.cu", "state_mixers.cu", "latent_moe.cu", "grouped_gemm_tc.cu", "rotary_latent.cu", "streams_mixers.cu"]
 CORE_HEADERS = ["common.cuh", "kernels.h", "attention_args.h", "status.h", "tma_util.cuh", "attention_tc.cuh"]
 
 _core = None

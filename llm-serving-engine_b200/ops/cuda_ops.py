@@ -675,9 +675,12 @@ class CudaOps:
         return out
 
     def decay_linear_attention(self, proj, *, num_heads, key_dim, value_dim, decay, state, step,
-                               activation, key_scale, cos, sin):
+                               activation, key_scale, cos, sin, decay_logits=None, decay_root=1.0,
+                               query_scale=1.0):
         """Portions longer than the kernel's chunk run as chunks side by side (three launches and
-        a scratch for the chunks' states); steps of single tokens and short portions are one launch."""
+        a scratch for the chunks' states); steps of single tokens and short portions are one launch.
+        With ``decay_logits`` (float32 ``[T, heads * key_dim]``; ``decay`` is then None) the decay of
+        key channel i at token t is ``sigmoid(z)^(1 / decay_root)``. ``query_scale`` multiplies q."""
         T = proj.shape[0]
         out = torch.empty(T, num_heads * value_dim, dtype=torch.float32, device=proj.device)
         L = self._la_chunk = getattr(self, "_la_chunk", None) or int(self.ext.linear_attention_chunk())
@@ -686,7 +689,9 @@ class CudaOps:
         max_chunks = max(1, -(-longest // L))
         scratch = None
         if max_chunks > 1:
-            need = (T // L + int(step.cu_q.shape[0]) - 1) * num_heads * value_dim * key_dim
+            # a chunk's state, and with decays per channel the product of its decays behind them
+            per_chunk = num_heads * (value_dim * key_dim + (key_dim if decay_logits is not None else 0))
+            need = (T // L + int(step.cu_q.shape[0]) - 1) * per_chunk
             scratch = getattr(self, "_la_scratch", None)
             if scratch is None or scratch.numel() < need:
                 if torch.cuda.is_current_stream_capturing():
@@ -697,7 +702,8 @@ class CudaOps:
                 scratch = self._la_scratch = torch.empty(need, dtype=torch.float32, device=proj.device)
         self.ext.decay_linear_attention(proj, out, state, decay, step.cu_q, step.ctx_lens, step.state_slots,
                                         num_heads, key_dim, value_dim, cos, sin, activation == "silu",
-                                        float(key_scale), max_chunks, scratch)
+                                        float(key_scale), max_chunks, scratch, decay_logits, float(decay_root),
+                                        float(query_scale))
         self.launches += 3 if max_chunks > 1 else 1
         return out
 
@@ -707,6 +713,75 @@ class CudaOps:
                                   gate_activation == "sigmoid", out)
         self.launches += 1
         return out
+
+    # ------------------------------------------------------------------ residual streams
+    def streams_spread(self, x, streams, scale=1.0):
+        """``[T, W]`` float32 to ``[T, streams * W]``: every stream is ``x * scale``."""
+        out = torch.empty(x.shape[0], streams * x.shape[1], dtype=torch.float32, device=x.device)
+        self.ext.streams_spread(x, out, int(streams), float(scale))
+        self.launches += 1
+        return out
+
+    def streams_read_norm(self, x, read, weight, eps, streams, out_dtype, rows=None):
+        """``u = sum_s read[s] x_s`` of each token (or of the listed rows), RMS-normed with
+        ``weight``, in ``out_dtype``."""
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty(n, x.shape[1] // streams, dtype=out_dtype, device=x.device)
+        self.ext.streams_read_norm(x, read, weight, float(eps), out, int(streams), rows)
+        self.launches += 1
+        return out
+
+    def streams_write(self, x, y, scale, mix, out, streams, then_read=None, then_weight=None, then_eps=0.0,
+                      out_dtype=None):
+        """``x_t <- sum_s mix[s, t] x_s + out[t] * scale * y`` for all streams of every token, in
+        place. With ``then_read``: the same launch also returns the read and norm of the new
+        streams (what the next sublayer reads). ``y``: a tensor ``[T, W]``, or a product whose
+        sums have not been taken yet."""
+        sums = None
+        if isinstance(y, DeferredProduct):
+            if y.sums is not None and (x.shape[1] // streams) % 4 == 0:
+                sums, y.sums = y.sums, None
+                y = sums
+            else:
+                y = y.resolve()
+        h = None
+        if then_read is not None:
+            h = torch.empty(x.shape[0], x.shape[1] // streams, dtype=out_dtype, device=x.device)
+        self.ext.streams_write(x, y, scale, mix, out, int(streams), then_read, then_weight, float(then_eps), h)
+        self.launches += 1
+        if sums is not None:
+            self._sums_taken(sums)
+        return h
+
+    # ------------------------------------------------------------------ rows of q, k, v prepared a token at a time
+    def qkv_norm_rope_write(self, qkv, *, num_heads, num_kv_heads, num_value_heads, head_dim, value_dim, out_dim,
+                            q_weight, k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,
+                            block_tables, page_tokens, out_dtype, temp_coef=0.0, temp_every=0):
+        """Of the float32 projection ``qkv`` (query heads, key heads, then ``num_value_heads`` value
+        heads; 0: a key head's value is its key as projected): RMS norm over all of a token's
+        query values and over all of its key values (if weights of those sizes are given), a query
+        factor ``1 + temp_coef * ln((pos + 1) // temp_every + 1)``, rotation of the first dims of
+        each head that the tables cover, heads filled up to ``out_dim`` with zeros, key/value page
+        write (a value head goes to ``num_kv_heads / num_value_heads`` key heads' pages). Returns
+        the queries ``[T, num_heads * out_dim]``."""
+        q = torch.empty(qkv.shape[0], num_heads * out_dim, dtype=out_dtype, device=qkv.device)
+        self.ext.qkv_norm_rope_write(qkv, q, int(num_heads), int(num_kv_heads), int(num_value_heads), int(head_dim),
+                                     int(value_dim), int(out_dim), q_weight, k_weight, float(eps), float(temp_coef),
+                                     int(temp_every), positions, token_seq, cos, sin, k_pages, v_pages,
+                                     block_tables, int(page_tokens))
+        self.launches += 1
+        return q
+
+    def differential_combine(self, a, proj, *, gate_col0, num_heads, group, head_dim, value_dim, lam, eps,
+                             out_scale, out_dtype):
+        """``a [T, 2 * heads * head_dim]`` (per key group: its heads' first maps, then their second
+        ones) to ``[T, heads * value_dim]``: ``o = a1 - lam * a2``, divided by its root mean square,
+        times ``out_scale`` and ``sigmoid(proj[t, gate_col0 + head])``."""
+        out = torch.empty(a.shape[0], num_heads * value_dim, dtype=a.dtype, device=a.device)
+        self.ext.differential_combine(a, proj, int(gate_col0), int(num_heads), int(group), int(head_dim),
+                                      int(value_dim), float(lam), float(eps), float(out_scale), out)
+        self.launches += 1
+        return out if out.dtype == out_dtype else out.to(out_dtype)
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):

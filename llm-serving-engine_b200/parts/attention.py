@@ -298,7 +298,7 @@ class PagedAttention(Mixer):
             num_value_heads=0 if s.values_are_keys else s.num_kv_heads, head_dim=s.head_dim,
             value_dim=self.value_dim, out_dim=self.kernel_dim,
             q_weight=self.q_norm_weight if normed else None, k_weight=self.k_norm_weight if normed else None,
-            eps=s.qk_norm_eps or 0.0, norm_rows=s.qk_norm_scope == "row",
+            eps=s.qk_norm_eps or 0.0,
             positions=step.positions, token_seq=step.token_seq, cos=cos, sin=sin,
             k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,
             block_tables=tables, page_tokens=cache.page_tokens, out_dtype=self.env.dtype)

@@ -109,7 +109,7 @@ class DifferentialAttention(Mixer):
         q = ops.qkv_norm_rope_write(
             qkv, num_heads=2 * s.num_heads, num_kv_heads=2 * s.num_kv_heads, num_value_heads=s.num_kv_heads,
             head_dim=s.head_dim, value_dim=s.value_dim, out_dim=self.kernel_dim,
-            q_weight=None, k_weight=None, eps=0.0, norm_rows=False,
+            q_weight=None, k_weight=None, eps=0.0,
             temp_coef=s.temp_coef, temp_every=s.temp_every,
             positions=step.positions, token_seq=step.token_seq, cos=None, sin=None,
             k_pages=cache.k if cache.writes else None, v_pages=cache.v if cache.writes else None,

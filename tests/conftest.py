@@ -382,3 +382,109 @@ def write_rirovik(folder, name):
 @pytest.fixture(scope="session")
 def rirovik_dirs(tmp_path_factory):
     return {name: write_rirovik(tmp_path_factory.mktemp(f"rirovik-{name}"), name) for name in RIROVIK_TINY}
+
+
+# ----------------------------------------------------------------------------- Lanilorn
+def _latt(heads, kv, dim, scale, mlp, window=0, rot=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": scale}
+    if window:
+        m["mask"] = {"size": window}
+    if rot:
+        m["rot"] = rot
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def _ldiff(heads, kv, dim, vdim, scale, diff, mlp, q_temp=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale, "diff": diff}
+    if q_temp:
+        m["q_temp"] = {"coef": q_temp[0], "every": q_temp[1]}
+    return {"type": "attention_2", "mixer": m, "mlp": mlp}
+
+
+def _lgla(heads, dim, vdim, tau, rank, mlp):
+    return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau, "decay_rank": rank}, "mlp": mlp}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+LANILORN_TINY = {
+    # two streams; a window shorter than a page with a third of each head rotated under stretched
+    # frequencies; grouped key heads in both attention kinds; a layer without feed-forward
+    "L1": dict(seed=4, page_tokens=16, config={
+        "architecture": "Lanilorn", "vocab": 157, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5},
+        "logit_scale": 0.5, "streams": 2,
+        "layers": [_latt(4, 2, 32, 0.2, _dense(96), window=10,
+                         rot={"base": 10000.0, "dims": 12, "scaling": {"factor": 4.0, "fast": 16.0, "original": 64, "slow": 2.0}}),
+                   _lgla(2, 16, 24, 8.0, 8, None),
+                   _ldiff(4, 2, 16, 32, 0.3, 0.3, _dense(80), q_temp=(0.4, 8)),
+                   _lgla(3, 32, 16, 2.0, 4, _dense(48))]}),
+    # sizes that are multiples of nothing; four streams; pages of 8 tokens; whole heads rotated
+    # without stretching; one key head per query head, and one for all; keys wider than values
+    "L2": dict(seed=9, page_tokens=8, config={
+        "architecture": "Lanilorn", "vocab": 130, "width": 72, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.7},
+        "logit_scale": 3.0, "streams": 4,
+        "layers": [_lgla(3, 20, 12, 16.0, 5, _dense(50)),
+                   _latt(3, 3, 24, 0.25, None, window=21, rot={"base": 500.0, "dims": 24}),
+                   _ldiff(3, 1, 40, 24, 0.15, 0.7, None, q_temp=(1.0, 3)),
+                   _latt(2, 1, 18, 0.3, _dense(30), window=3, rot={"base": 50.0, "dims": 6}),
+                   _ldiff(2, 2, 10, 50, 0.4, 0.2, _dense(64))]}),
+    # one stream; attention that sees everything and has no rotation; a window of one token; no
+    # query temperature; a root of one
+    "L3": dict(seed=21, page_tokens=16, config={
+        "architecture": "Lanilorn", "vocab": 99, "width": 48, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+        "logit_scale": 1.0, "streams": 1,
+        "layers": [_latt(2, 2, 16, 0.3, _dense(64)),
+                   _ldiff(2, 1, 16, 16, 0.25, 0.5, None),
+                   _lgla(1, 48, 64, 1.0, 3, _dense(32)),
+                   _latt(6, 2, 16, 0.3, None, window=1, rot={"base": 100.0, "dims": 16,
+                         "scaling": {"factor": 16.0, "fast": 4.0, "original": 32, "slow": 0.5}})]}),
+}
+
+
+def write_lanilorn(folder, name):
+    """A random model folder whose queries and keys are sharp and whose small tensors (norm weights,
+    stream weights, scales per channel, sinks, decay biases, the weights of the second map) differ
+    clearly from one another, so that leaving one of them out, a key too many or a lost state
+    changes the logits clearly."""
+    from safetensors.torch import load_file, save_file
+
+    from llmserve_b200.config.lanilorn import LanilornConfig
+    from llmserve_b200.weights import write_random_model
+
+    spec = LANILORN_TINY[name]
+    write_random_model(folder, LanilornConfig.from_dict(spec["config"]), spec["seed"])
+    f = folder / "model.safetensors"
+    t = load_file(str(f))
+    g = torch.Generator().manual_seed(spec["seed"] + 1)
+    n = spec["config"]["streams"]
+    for k, v in t.items():
+        r = torch.rand(v.shape, generator=g)
+        if k.endswith(".mix") and v.dim() == 2 and ".hc" in k:
+            t[k] = (torch.eye(n) * 0.8 + (r - 0.3) * 0.5).to(v.dtype)
+        elif ".hc" in k:  # read and write weights
+            t[k] = (0.4 + r).to(v.dtype) * (1 if k.endswith(".in") else -1)
+        elif k.endswith(".sink"):
+            t[k] = (4 * r - 1).to(v.dtype)
+        elif k.endswith("a2.b"):
+            t[k] = (5 * r - 1).to(v.dtype)
+        elif k.endswith((".lq1", ".lk1", ".lq2", ".lk2")):
+            t[k] = (0.6 * (r - 0.5)).to(v.dtype)
+        elif v.dim() == 1:  # norm weights, scales per channel
+            t[k] = (0.5 + r).to(v.dtype)
+        elif k == "embed":
+            t[k] = (v.float() * 40).to(v.dtype)
+        elif k.endswith(("mix.q", "mix.k")):
+            t[k] = (v.float() * spec.get("sharp", 10)).to(v.dtype)
+        elif k.endswith(("mix.a1", "mix.a2")):
+            t[k] = (v.float() * 25).to(v.dtype)
+        else:
+            t[k] = (v.float() * 8).to(v.dtype)
+    save_file(t, str(f))
+    return folder
+
+
+@pytest.fixture(scope="session")
+def lanilorn_dirs(tmp_path_factory):
+    return {name: write_lanilorn(tmp_path_factory.mktemp(f"lanilorn-{name}"), name) for name in LANILORN_TINY}

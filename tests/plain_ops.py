@@ -420,7 +420,7 @@ class PlainOps:
 
     # ------------------------------------------------------------------ rows of q, k, v prepared a token at a time
     def qkv_norm_rope_write(self, qkv, *, num_heads, num_kv_heads, num_value_heads, head_dim, value_dim, out_dim,
-                            q_weight, k_weight, eps, norm_rows, positions, token_seq, cos, sin, k_pages,
+                            q_weight, k_weight, eps, positions, token_seq, cos, sin, k_pages,
                             v_pages, block_tables, page_tokens, out_dtype, temp_coef=0.0, temp_every=0):
         T, D, Dv, Dp = qkv.shape[0], head_dim, value_dim, out_dim
         nq, nk, nv = num_heads, num_kv_heads, num_value_heads
@@ -428,12 +428,8 @@ class PlainOps:
         q, k = p[:, : nq * D], p[:, nq * D : (nq + nk) * D]
         v = k.reshape(T, nk, D) if nv == 0 else p[:, (nq + nk) * D : (nq + nk) * D + nv * Dv].reshape(T, nv, Dv)
         if q_weight is not None:
-            if norm_rows:
-                q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
-                k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
-            else:
-                q = (q.reshape(T, nq, D) * torch.rsqrt(q.reshape(T, nq, D).pow(2).mean(-1, keepdim=True) + eps) * q_weight).reshape(T, -1)
-                k = (k.reshape(T, nk, D) * torch.rsqrt(k.reshape(T, nk, D).pow(2).mean(-1, keepdim=True) + eps) * k_weight).reshape(T, -1)
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight
         pos = positions.long()
         if temp_every:
             q = q * (1.0 + temp_coef * torch.log(torch.floor((pos.float() + 1.0) / temp_every) + 1.0))[:, None]
