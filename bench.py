@@ -19,7 +19,9 @@ and a float32 replay of one 8192-token sequence against the plain implementation
 reference's own harness (src/llmserve/bench/run.py:96,124-176): fixed output lengths, greedy, a
 warm-up run that is thrown away, one JSON line with the environment.
 
-``--workload designs`` (``--arms llama,gubotar,pazivik,rirovik``) puts four Pazivik layers (latent attention
+``--workload designs`` (``--arms llama,gubotar,pazivik,rirovik,lanilorn``) puts four Lanilorn layers (four
+residual streams; linear attention with a decay per channel and token, windowed attention with sinks and
+a norm over whole rows, differential attention; ungated dense feed-forwards), four Pazivik layers (latent attention
 with a window; dense and routed feed-forwards), four Gubotar layers (parallel, retention, retention, parallel) and
 four Rirovik layers (latent attention with a query latent and a rotated key part, without and with a window;
 attention that keeps the first keys; routed ungated experts everywhere) beside
@@ -634,6 +636,31 @@ def rirovik_layers(width, heads, kv_heads, head_dim, ff, rank=96, rot_dim=32, wi
     return [latent("latent_attention_2"), latent("latent_attention"), plain, latent("latent_attention", 1)]
 
 
+def lanilorn_layers(width, heads, kv_heads, head_dim, ff, window=1024, state_dim=128, rank=64):
+    """Four Lanilorn layers at a Llama layer's sizes: linear attention with a decay per channel and
+    token on heads of ``state_dim`` x ``state_dim``; the Llama layer's grouped heads with a window,
+    half of each head rotated under stretched frequencies, sinks and a gate per head; differential
+    attention with half as many heads of twice the value size (as many softmax maps as the Llama
+    layer has heads); the windowed kind again. Every feed-forward is ungated, of the Llama
+    layer's size."""
+    mlp = {"kind": "dense", "ff": ff}
+    lin = max(1, width // state_dim)
+    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": lin, "dim": state_dim, "vdim": state_dim, "tau": 16.0,
+                                                 "decay_rank": rank}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+        "mask": {"size": window},
+        "rot": {"base": 250000.0, "dims": head_dim // 2,
+                "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}}}}
+    half, kv_half = max(1, heads // 2), max(1, kv_heads // 2)
+    while half % kv_half:
+        kv_half -= 1
+    diff = {"type": "attention_2", "mlp": mlp, "mixer": {
+        "heads": half, "kv_heads": kv_half, "dim": head_dim, "vdim": 2 * head_dim, "scale": head_dim ** -0.5,
+        "diff": 0.5, "q_temp": {"coef": 0.1, "every": 256}}}
+    return [gla, att, diff, att]
+
+
 def kernel_profile(fn, reps=3) -> dict:
     """Device time of ``fn()`` by kernel, from the framework's profiler: microseconds per call."""
     import collections
@@ -677,6 +704,8 @@ def designs_main(args) -> int:
                                                  "layers": pazivik_layers(w, heads, hd, ff)}),
             "rirovik": ("random:rirovik-2048", {"width": w, "vocab": ll["vocab_size"],
                                                  "layers": rirovik_layers(w, heads, kv, hd, ff)}),
+            "lanilorn": ("random:lanilorn-2048", {"width": w, "vocab": ll["vocab_size"],
+                                                   "layers": lanilorn_layers(w, heads, kv, hd, ff, state_dim=hd if w < 2048 else 128)}),
         }
         arms = {k: v for k, v in arms.items() if k in args.arms.split(",")}
         row = {"sizes": f"{alias}: width {w}, ff {ff}, {heads} heads of {hd}, 4 layers"}
@@ -828,7 +857,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "continuous", "long", "designs"])
-    ap.add_argument("--arms", default="llama,gubotar,pazivik,rirovik",
+    ap.add_argument("--arms", default="llama,gubotar,pazivik,rirovik,lanilorn",
                     help="--workload designs: which architectures run side by side")
     ap.add_argument("--model", default="smollm2-1.7b")
     ap.add_argument("--batch", type=int, default=8)

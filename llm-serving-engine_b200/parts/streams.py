@@ -155,9 +155,17 @@ class StreamsBlock(Block):
         if pending is not None and not isinstance(pending, PendingStreamsWrite):
             raise TypeError("a streams block follows only blocks that leave their add as a pending streams write")
         h = self.norm_in.forward(x, pending)
-        y = self.mixer.forward(h, step, cache)
+        # a sublayer's output projection may come back as sums still to be taken: the write takes them
+        if getattr(self.mixer, "accepts_deferral", False):
+            y = self.mixer.forward(h, step, cache, may_defer=True)
+        else:
+            y = self.mixer.forward(h, step, cache)
         first = self.mixer_write.pending(x, y)
         if self.feed_forward is None:
             return x, first
         h = self.norm_post.forward(x, first)
-        return x, self.ff_write.pending(x, self.feed_forward.forward(h, step))
+        if getattr(self.feed_forward, "accepts_residual", False):
+            f = self.feed_forward.forward(h, step, may_defer=True)
+        else:
+            f = self.feed_forward.forward(h, step)
+        return x, self.ff_write.pending(x, f)
