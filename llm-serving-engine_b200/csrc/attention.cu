@@ -1309,6 +1309,7 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
     }
     const int h = h0 + gq;
     if (a.num_splits == 1) {
+      if (a.sinks && L > 0.f) L += Exp<T>::f(a.sinks[h] - M);  // a sink joins the denominator once
       T* op = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
       op[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
     } else {
@@ -1352,7 +1353,8 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   if (FUSED) clear_sums();
   merge_partitions<T, HEADS>(
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
-      a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
+      a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D,
+      a.sinks ? a.sinks + h0 : nullptr);  // after the merge, once
 }
 
 // The same computation fed by TMA: every warp has PER slots of 128-byte-swizzled shared memory, each
@@ -1647,8 +1649,9 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
-  const bool options = a->head_scale || a->slopes || a->chunk > 0 || a->sinks ||
-                       (a->keep_first > 0 && a->window > 0);  // served by the CUDA-core kernel only
+  // served by the CUDA-core kernel only (sinks: also by the tensor-core kernel for groups of up to 8)
+  const bool options = a->head_scale || a->slopes || a->chunk > 0 || (a->sinks && G > 8) ||
+                       (a->keep_first > 0 && a->window > 0);
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
   // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
   // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
@@ -1677,7 +1680,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     // partitions: 30.6 against 27.3) the other one is taken.
     const bool ring_can = G <= 8 && ps >= 4 && pool_rows > 0 && pool_rows < (1LL << 31);
     if (a->qkv_sums && G > 8) return LSE_BAD_ARGUMENT;  // only the kernel for groups of up to 8 makes its own queries
-    if (ring_can && !a->qkv_sums && (a->force_simt == 3 ||
+    if (ring_can && !a->qkv_sums && !a->sinks && (a->force_simt == 3 ||
                      (a->force_simt == 0 && a->num_splits == 1 && blocks >= 10LL * sms))) {
       constexpr int PER = 1;
       constexpr int smem = PER * DEC_WARPS * 2 * ring::TILE_BYTES + 1024;

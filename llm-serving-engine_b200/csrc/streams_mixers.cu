@@ -100,7 +100,8 @@ streams_read_norm_kernel(const float* __restrict__ x, const float* __restrict__ 
 // ------------------------------------------------------------------------------------ write (+ read + norm)
 // One block per token. TY: the sublayer's result as float32, bfloat16, or the fixed-point sums of
 // a few-rows product (taken: zeros are left behind).
-template <typename TY, typename TO, int V>
+// MS: the most streams this instantiation holds in registers (S <= MS).
+template <typename TY, typename TO, int V, int MS>
 __global__ void __launch_bounds__(SM_THREADS)
 streams_write_kernel(float* __restrict__ x, const TY* y, const float* __restrict__ scale,
                      const float* __restrict__ mix, const float* __restrict__ outw, int W, int S,
@@ -122,9 +123,9 @@ streams_write_kernel(float* __restrict__ x, const TY* y, const float* __restrict
   const TY* yr = y + t * (size_t)W;
   float ss = 0.f;
   for (int i = threadIdx.x * V; i < W; i += SM_THREADS * V) {
-    float xs[SM_MAX_STREAMS][V], yv[V];
+    float xs[MS][V], yv[V];
 #pragma unroll
-    for (int s = 0; s < SM_MAX_STREAMS; ++s)
+    for (int s = 0; s < MS; ++s)
       if (s < S) ld_vec<float, V>(xr + (size_t)s * W + i, xs[s]);
     ld_vec<TY, V>(yr + i, yv);
     if (scale) {
@@ -137,13 +138,13 @@ streams_write_kernel(float* __restrict__ x, const TY* y, const float* __restrict
 #pragma unroll
     for (int j = 0; j < V; ++j) u[j] = 0.f;
 #pragma unroll
-    for (int r = 0; r < SM_MAX_STREAMS; ++r) {
+    for (int r = 0; r < MS; ++r) {
       if (r < S) {
         float nv[V];
 #pragma unroll
         for (int j = 0; j < V; ++j) nv[j] = ow[r] * yv[j];
 #pragma unroll
-        for (int s = 0; s < SM_MAX_STREAMS; ++s)
+        for (int s = 0; s < MS; ++s)
           if (s < S) {
 #pragma unroll
             for (int j = 0; j < V; ++j) nv[j] = fmaf(m[s * S + r], xs[s][j], nv[j]);
@@ -198,7 +199,11 @@ struct QkvRowsArgs {
   int table_stride, page_tokens;
 };
 
-template <typename T>
+// One token per blockIdx.x; the token's heads are shared by the gridDim.y blocks of that token (few
+// tokens: many blocks each), every one of which forms the two sums of squares itself. A thread's
+// unit of work is VEC consecutive dims of one head (4: every row, head and rotated half holds
+// whole 16-byte vectors; 1: any sizes).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(SM_THREADS) qkv_norm_rope_write_kernel(const QkvRowsArgs a) {
   __shared__ float scratch[32];
   pdl_trigger();
@@ -216,52 +221,85 @@ __global__ void __launch_bounds__(SM_THREADS) qkv_norm_rope_write_kernel(const Q
   float inv_q = 1.f, inv_k = 1.f;
   if (a.qw) {
     float sq = 0.f, sk = 0.f;
-    for (int i = threadIdx.x; i < nq * D; i += SM_THREADS) sq += row[i] * row[i];
-    for (int i = threadIdx.x; i < nk * D; i += SM_THREADS) sk += row[nq * D + i] * row[nq * D + i];
+    for (int i = threadIdx.x * VEC; i < nq * D; i += SM_THREADS * VEC) {
+      float v[VEC];
+      ld_vec<float, VEC>(row + i, v);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) sq += v[j] * v[j];
+    }
+    for (int i = threadIdx.x * VEC; i < nk * D; i += SM_THREADS * VEC) {
+      float v[VEC];
+      ld_vec<float, VEC>(row + nq * D + i, v);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) sk += v[j] * v[j];
+    }
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
     inv_q = rsqrtf(sq / (float)(nq * D) + a.eps);
     inv_k = rsqrtf(sk / (float)(nk * D) + a.eps);
   }
-  if (a.temp_every > 0)
-    inv_q *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+  if (a.temp_every > 0) inv_q *= 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
   const int half = a.rot / 2;
   const float* cr = a.cos ? a.cos + (size_t)pos * half : nullptr;
   const float* sr = a.cos ? a.sin + (size_t)pos * half : nullptr;
   T* q_out = (T*)a.q_out + (size_t)t * nq * Dp;
   T* k_pages = (T*)a.k_pages;
   T* v_pages = (T*)a.v_pages;
-  const int heads = a.k_pages ? nq + nk : nq;
-  for (int idx = threadIdx.x; idx < heads * Dp; idx += SM_THREADS) {
-    const int h = idx / Dp, i = idx - h * Dp;
-    const bool is_q = h < nq;
-    float v = 0.f;
-    if (i < D) {
-      const float* src = row + (size_t)h * D;  // the key heads follow the query heads
-      const float* w = a.qw ? (is_q ? a.qw + (size_t)h * D : a.kw + (size_t)(h - nq) * D) : nullptr;
-      const float inv = is_q ? inv_q : inv_k;
-      v = src[i] * inv * (w ? w[i] : 1.f);
-      if (i < a.rot) {
-        const int ip = i < half ? i + half : i - half;
-        const float vp = src[ip] * inv * (w ? w[ip] : 1.f);
-        const int f = i < half ? i : i - half;
-        v = i < half ? v * cr[f] - vp * sr[f] : v * cr[f] + vp * sr[f];
-      }
-    }
-    if (is_q) q_out[idx] = Num<T>::from_float(v);
-    else k_pages[(page_row + (size_t)(h - nq) * a.page_tokens) * Dp + i] = Num<T>::from_float(v);
-  }
-  if (!a.v_pages) return;
+  const int per_head = Dp / VEC;
+  const int qk_units = (a.k_pages ? nq + nk : nq) * per_head;
+  const int units = qk_units + (a.v_pages ? nk * per_head : 0);
   const int repeat = a.nv > 0 ? nk / a.nv : 1;
-  for (int idx = threadIdx.x; idx < nk * Dp; idx += SM_THREADS) {
-    const int h = idx / Dp, i = idx - h * Dp;
-    float v = 0.f;
-    if (a.nv == 0) {
-      if (i < D) v = row[(size_t)(nq + h) * D + i];
-    } else if (i < a.Dv) {
-      v = row[(size_t)(nq + nk) * D + (size_t)(h / repeat) * a.Dv + i];
+  for (int u = blockIdx.y * SM_THREADS + threadIdx.x; u < units; u += gridDim.y * SM_THREADS) {
+    float v[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) v[j] = 0.f;
+    if (u < qk_units) {
+      const int h = u / per_head, i = (u - h * per_head) * VEC;
+      const bool is_q = h < nq;
+      if (i < D) {
+        const float* src = row + (size_t)h * D;  // the key heads follow the query heads
+        const float* w = a.qw ? (is_q ? a.qw + (size_t)h * D : a.kw + (size_t)(h - nq) * D) : nullptr;
+        const float inv = is_q ? inv_q : inv_k;
+        ld_vec<float, VEC>(src + i, v);
+        if (w) {
+          float wv[VEC];
+          ld_vec<float, VEC>(w + i, wv);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) v[j] *= wv[j];
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] *= inv;
+        if (i < a.rot) {
+          const int ip = i < half ? i + half : i - half, f = i < half ? i : i - half;
+          float vp[VEC], c[VEC], sn[VEC];
+          ld_vec<float, VEC>(src + ip, vp);
+          if (w) {
+            float wv[VEC];
+            ld_vec<float, VEC>(w + ip, wv);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) vp[j] *= wv[j];
+          }
+          ld_vec<float, VEC>(cr + f, c);
+          ld_vec<float, VEC>(sr + f, sn);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            const float p = vp[j] * inv;
+            v[j] = i < half ? v[j] * c[j] - p * sn[j] : v[j] * c[j] + p * sn[j];
+          }
+        }
+      }
+      T* dst = is_q ? q_out + (size_t)h * Dp + i : k_pages + (page_row + (size_t)(h - nq) * a.page_tokens) * Dp + i;
+      st_vec<T, VEC>(dst, v);
+    } else {
+      const int uv = u - qk_units;
+      const int h = uv / per_head, i = (uv - h * per_head) * VEC;
+      if (a.nv == 0) {
+        if (i < D) ld_vec<float, VEC>(row + (size_t)(nq + h) * D + i, v);
+      } else if (i < a.Dv) {
+        ld_vec<float, VEC>(row + (size_t)(nq + nk) * D + (size_t)(h / repeat) * a.Dv + i, v);
+      }
+      st_vec<T, VEC>(v_pages + (page_row + (size_t)h * a.page_tokens) * Dp + i, v);
     }
-    v_pages[(page_row + (size_t)h * a.page_tokens) * Dp + i] = Num<T>::from_float(v);
   }
 }
 
@@ -360,11 +398,17 @@ extern "C" int lse_streams_write(float* x, const void* y, int y_dtype, const flo
   if (y_dtype == LSE_FIXED64 && !wide) return LSE_BAD_ARGUMENT;
   const size_t smem = then_read ? (size_t)W * sizeof(float) : 0;
   if (!then_read) out_dtype = LSE_F32;
-#define LSE_SW(TY, TO, V)                                                                                  \
-  do {                                                                                                     \
-    if (allow_row(streams_write_kernel<TY, TO, V>, smem) != LSE_OK) return LSE_LAUNCH_FAILED;              \
-    launch(streams_write_kernel<TY, TO, V>, T, SM_THREADS, smem, stream, x, (const TY*)y, scale, mix, outw, \
-           W, S, then_read, then_w, then_eps, (TO*)out);                                                   \
+#define LSE_SW_MS(TY, TO, V, MS)                                                                                \
+  do {                                                                                                          \
+    if (allow_row(streams_write_kernel<TY, TO, V, MS>, smem) != LSE_OK) return LSE_LAUNCH_FAILED;               \
+    launch(streams_write_kernel<TY, TO, V, MS>, T, SM_THREADS, smem, stream, x, (const TY*)y, scale, mix, outw, \
+           W, S, then_read, then_w, then_eps, (TO*)out);                                                        \
+  } while (0)
+#define LSE_SW(TY, TO, V)                                   \
+  do {                                                      \
+    if (V == 4 && S <= 2) LSE_SW_MS(TY, TO, V, 2);          \
+    else if (V == 4 && S <= 4) LSE_SW_MS(TY, TO, V, 4);     \
+    else LSE_SW_MS(TY, TO, V, SM_MAX_STREAMS);              \
   } while (0)
 #define LSE_SW_OUT(TY, V)                              \
   do {                                                 \
@@ -383,6 +427,7 @@ extern "C" int lse_streams_write(float* x, const void* y, int y_dtype, const flo
   }
 #undef LSE_SW_OUT
 #undef LSE_SW
+#undef LSE_SW_MS
   return LSE_CHECK_LAUNCH();
 }
 
@@ -404,9 +449,24 @@ extern "C" int lse_qkv_norm_rope_write(const float* proj, long long stride, int 
   a.positions = positions; a.token_seq = token_seq; a.cos = cos; a.sin = sin; a.rot = cos ? rot : 0;
   a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.block_tables = block_tables;
   a.table_stride = table_stride; a.page_tokens = page_tokens;
-  if (dtype == LSE_BF16) launch(qkv_norm_rope_write_kernel<bf16>, T, SM_THREADS, 0, stream, a);
-  else if (dtype == LSE_F32) launch(qkv_norm_rope_write_kernel<float>, T, SM_THREADS, 0, stream, a);
-  else return LSE_BAD_ARGUMENT;
+  // whole 16-byte vectors everywhere: rows, heads, value heads, rotated halves, cos/sin rows
+  const bool wide = stride % 4 == 0 && D % 4 == 0 && Dp % 4 == 0 && (nv == 0 || Dv % 4 == 0) && a.rot % 8 == 0;
+  const int units = ((k_pages ? nq + nk : nq) + (v_pages ? nk : 0)) * (Dp / (wide ? 4 : 1));
+  // few tokens: a token's heads are shared by several blocks, up to about four blocks per SM in all
+  int parts = (600 + T - 1) / T;
+  const int most = (units + SM_THREADS - 1) / SM_THREADS;
+  if (parts > most) parts = most;
+  if (parts < 1) parts = 1;
+  const dim3 grid(T, parts);
+  if (dtype == LSE_BF16) {
+    if (wide) launch(qkv_norm_rope_write_kernel<bf16, 4>, grid, SM_THREADS, 0, stream, a);
+    else launch(qkv_norm_rope_write_kernel<bf16, 1>, grid, SM_THREADS, 0, stream, a);
+  } else if (dtype == LSE_F32) {
+    if (wide) launch(qkv_norm_rope_write_kernel<float, 4>, grid, SM_THREADS, 0, stream, a);
+    else launch(qkv_norm_rope_write_kernel<float, 1>, grid, SM_THREADS, 0, stream, a);
+  } else {
+    return LSE_BAD_ARGUMENT;
+  }
   return LSE_CHECK_LAUNCH();
 }
 
