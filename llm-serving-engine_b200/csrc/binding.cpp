@@ -812,7 +812,7 @@ void decay_linear_attention(const Tensor& proj, Tensor& out, Tensor& state, cons
                                   cos ? cos->data_ptr<float>() : nullptr, sin ? sin->data_ptr<float>() : nullptr, rot,
                                   silu ? 1 : 0, (float)key_scale, (int)max_chunks, chunk_ptr, stream(),
                                   gate_z ? gate_z->data_ptr<float>() : nullptr, gate_z ? gate_z->size(1) : 0,
-                                  (float)decay_root, (float)query_scale, chunk_decay),
+                                  (float)decay_root, (float)query_scale, chunk_decay, (int)proj.size(0)),
        "decay_linear_attention");
 }
 

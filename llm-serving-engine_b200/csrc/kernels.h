@@ -171,9 +171,11 @@ int lse_decay_linear_attention(const float* proj, long long stride, float* out, 
                                float key_scale, int max_chunks, float* chunks, cudaStream_t stream,
                                // a decay per key channel and token, alpha = sigmoid(z)^(1/decay_root),
                                // z = gate_z[t, h*dk + i] (decay may then be null); q is multiplied by
-                               // query_scale; chunk_decay: scratch of (chunks as above) * H * dk floats
+                               // query_scale; chunk_decay: scratch of (chunks as above) * H * dk floats.
+                               // total_rows: rows of proj and gate_z. With max_chunks > 1 and total_rows > 0
+                               // gate_z is overwritten with the decays (it is the caller's temporary).
                                const float* gate_z = nullptr, long long gate_stride = 0, float decay_root = 1.f,
-                               float query_scale = 1.f, float* chunk_decay = nullptr);
+                               float query_scale = 1.f, float* chunk_decay = nullptr, int total_rows = 0);
 // ---- several residual streams, rows of q/k/v prepared a token at a time, differential attention
 // (streams_mixers.cu). The residual state is float32 [T, S * W]: a token's S streams of W values.
 

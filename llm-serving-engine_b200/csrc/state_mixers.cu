@@ -393,6 +393,7 @@ __global__ void norm_rope_kv_write_kernel(const float* __restrict__ qkv, T* __re
 // A portion of at most L tokens (a single token, above all) is one chunk: launch A alone, which
 // then reads and writes the request's state itself.
 constexpr int LA_RPT = 8, LA_TT = 16, LA_THREADS = 256, LA_PAD = 4;
+constexpr int LA_TT_GATED = 8;  // tokens per tile with decays per channel: a third array is staged beside q and k
 
 struct LinAttnArgs {
   const float* proj;      // [T, stride]: q | k | v | ... per row, heads concatenated
@@ -415,7 +416,8 @@ struct LinAttnArgs {
   const float* gate_z;    // [T, gate_stride], heads x dk logits per row; null: the fixed decays
   long long gate_stride;
   float inv_root;
-  float query_scale;      // q is multiplied by this
+  float query_scale;      // the outputs are multiplied by this (a factor on q)
+  int gate_is_logit;      // 1: gate_z holds logits; 0: it holds the decays themselves
   float* chunk_decay;     // scratch [chunks of all chunked sequences, H, dk]: the product of a chunk's alphas
 };
 
@@ -444,11 +446,15 @@ __device__ __forceinline__ void la_copy(float* smem, const float* gmem, bool wid
 // this one is computed: two buffers); activation, rotation and the key's scale are then applied
 // in place. Row i of a token's q (or k) lies at (i / RPT) * (RPT + PAD) + i % RPT: the pad keeps
 // the 16-byte reads of the P lanes of a column on different banks.
-// GATED: the decay of row i at token t is alpha_t[i] (its logits are staged like q and k and turned
-// into alphas in place); launch A also leaves the product of each chunk's alphas for launch B, and
-// launch C carries the running product of the chunk's alphas per row instead of a power of the decay.
-template <int P, bool GATED>
-__global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(const LinAttnArgs a) {
+// MODE 0: a fixed decay per head (launch A or C by a.phase). MODE 1 and 2: launches A and C with a
+// decay per row and token, alpha_t[i]: its logits are staged like q and k and turned into alphas
+// in place; launch C carries the running product of the chunk's alphas per row instead of a power
+// of the decay. The product of each chunk's alphas, which launch B needs, is made by
+// chunk_decay_kernel.
+template <int P, int MODE>
+__global__ void __launch_bounds__(LA_THREADS, MODE == 0 ? 0 : 3) decay_linear_attention_kernel(const LinAttnArgs a) {
+  constexpr bool GATED = MODE != 0;
+  constexpr int TT = GATED ? LA_TT_GATED : LA_TT;
   extern __shared__ __align__(16) float la_smem[];
   pdl_trigger();
   constexpr int CB = 2 * LA_THREADS / P;
@@ -458,7 +464,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   const int seq = blockIdx.z;
   const int r0 = a.cu_q[seq], n = a.cu_q[seq + 1] - r0;
   const int num_chunks = (n + L - 1) / L;
-  const bool add_pass = a.phase == 2;
+  const bool add_pass = MODE == 0 ? a.phase == 2 : MODE == 2;
   const int c = blockIdx.y + (add_pass ? 1 : 0);
   if (c >= num_chunks) {
     pdl_wait();  // no block leaves before the kernels before this one are done: the next kernel counts on it
@@ -470,7 +476,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   const int j = cb * CB + jl;  // this thread's columns: j and j + 1
   constexpr int ldq = P * (LA_RPT + LA_PAD);
   // q [TT][ldq], k [TT][ldq], v [TT][CB], and with GATED the alphas [TT][ldq]
-  constexpr int per_buf = (GATED ? 3 : 2) * LA_TT * ldq + LA_TT * CB;
+  constexpr int per_buf = (GATED ? 3 : 2) * TT * ldq + TT * CB;
   const float decay = GATED ? 1.f : a.decay[h];
   float S[LA_RPT], S1[LA_RPT];
   const bool has0 = j < dv, has1 = j + 1 < dv;
@@ -493,9 +499,9 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   pdl_wait();
   auto issue = [&](int buf, int t0) {
     float* qs = la_smem + buf * per_buf;
-    float* ks = qs + LA_TT * ldq;
-    float* vs = ks + LA_TT * ldq;
-    const int tn = min(LA_TT, t_end - t0);
+    float* ks = qs + TT * ldq;
+    float* vs = ks + TT * ldq;
+    const int tn = min(TT, t_end - t0);
     for (int idx = threadIdx.x; idx < tn * qk_units; idx += LA_THREADS) {
       const int tt = idx / qk_units, i = (idx - tt * qk_units) * qk_step;
       const float* row = a.proj + (size_t)(r0 + t0 + tt) * a.stride + (size_t)h * dk + i;
@@ -503,7 +509,7 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
       la_copy(qs + at, row, wide_qk);
       if (!add_pass) la_copy(ks + at, row + (size_t)H * dk, wide_qk);
       if constexpr (GATED)
-        la_copy(vs + LA_TT * CB + at, a.gate_z + (size_t)(r0 + t0 + tt) * a.gate_stride + (size_t)h * dk + i, wide_qk);
+        la_copy(vs + TT * CB + at, a.gate_z + (size_t)(r0 + t0 + tt) * a.gate_stride + (size_t)h * dk + i, wide_qk);
     }
     if (!add_pass)
       for (int idx = threadIdx.x; idx < tn * v_units; idx += LA_THREADS) {
@@ -540,22 +546,22 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   float run[GATED ? LA_RPT : 1];  // GATED: the product of the chunk's alphas so far, row by row
 #pragma unroll
   for (int r = 0; r < (GATED ? LA_RPT : 1); ++r) run[r] = 1.f;
-  const bool keeps_run = GATED && (add_pass || (num_chunks > 1 && cb == 0 && threadIdx.x < P));
+  const bool keeps_run = MODE == 2;
   int buf = 0;
-  for (int t0 = t_begin; t0 < t_end; t0 += LA_TT, buf ^= 1) {
-    const int tn = min(LA_TT, t_end - t0);
-    if (t0 + LA_TT < t_end) {
-      issue(buf ^ 1, t0 + LA_TT);
+  for (int t0 = t_begin; t0 < t_end; t0 += TT, buf ^= 1) {
+    const int tn = min(TT, t_end - t0);
+    if (t0 + TT < t_end) {
+      issue(buf ^ 1, t0 + TT);
       asm volatile("cp.async.wait_group 1;\n" ::);
     } else {
       asm volatile("cp.async.wait_group 0;\n" ::);
     }
     __syncthreads();
     float* qs = la_smem + buf * per_buf;
-    float* ks = qs + LA_TT * ldq;
-    float* vs = ks + LA_TT * ldq;
-    float* gs = vs + LA_TT * CB;
-    if (a.silu || a.rot || a.key_scale != 1.f || a.query_scale != 1.f || GATED) {
+    float* ks = qs + TT * ldq;
+    float* vs = ks + TT * ldq;
+    float* gs = vs + TT * CB;
+    if (a.silu || a.rot || a.key_scale != 1.f || (GATED && a.gate_is_logit)) {
       for (int idx = threadIdx.x; idx < tn * work; idx += LA_THREADS) {
         const int tt = idx / work, w = idx - tt * work;
         const int i = w < half ? w : w + half;  // rows [half, rot) are done with their partners
@@ -575,16 +581,20 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
           }
           const size_t tab = (size_t)(pos0 + t0 + tt) * half + i;
           const float cs = a.cos[tab], sn = a.sin[tab];
-          qs[atp] = (qp * cs + q * sn) * a.query_scale;
+          qs[atp] = qp * cs + q * sn;
           ks[atp] = (kp * cs + k * sn) * a.key_scale;
-          if constexpr (GATED) gs[atp] = root_of_sigmoid(gs[atp], a.inv_root);
+          if constexpr (GATED) {
+            if (a.gate_is_logit) gs[atp] = root_of_sigmoid(gs[atp], a.inv_root);
+          }
           const float q2 = q * cs - qp * sn, k2 = k * cs - kp * sn;
           q = q2;
           k = k2;
         }
-        qs[at] = q * a.query_scale;
+        qs[at] = q;
         ks[at] = k * a.key_scale;
-        if constexpr (GATED) gs[at] = root_of_sigmoid(gs[at], a.inv_root);
+        if constexpr (GATED) {
+          if (a.gate_is_logit) gs[at] = root_of_sigmoid(gs[at], a.inv_root);
+        }
       }
       if (a.silu && !add_pass)
         for (int idx = threadIdx.x; idx < tn * cols; idx += LA_THREADS) {
@@ -661,25 +671,17 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
       if (writes) {
         // launch C adds into what launch A stored: a reduction without a return value, so that
         // the warp does not wait for the old value (one thread per element: the order is fixed)
-        if (add_pass) atomicAdd(dst, carried * acc);
-        else *dst = acc;
+        if (add_pass) atomicAdd(dst, carried * acc * a.query_scale);
+        else *dst = acc * a.query_scale;
       }
       if (P == 1 && has1) {
-        if (add_pass) atomicAdd(dst + 1, carried * acc1);
-        else dst[1] = acc1;
+        if (add_pass) atomicAdd(dst + 1, carried * acc1 * a.query_scale);
+        else dst[1] = acc1 * a.query_scale;
       }
     }
     __syncthreads();  // the buffer is free for the tile after the next
   }
   if (add_pass) return;
-  if constexpr (GATED) {
-    if (keeps_run) {  // the first P threads of the head's first slice hold every row once
-      float* dst = a.chunk_decay + ((size_t)(first_chunk + c) * H + h) * dk + p * LA_RPT;
-#pragma unroll
-      for (int r = 0; r < LA_RPT; ++r)
-        if (p * LA_RPT + r < dk) dst[r] = run[r];
-    }
-  }
   float* to = num_chunks > 1 ? chunk_states + (size_t)c * per_state : st;
   auto store_column = [&](const float (&src)[LA_RPT], float* dst) {
     if (dk % 4 == 0) {
@@ -696,6 +698,40 @@ __global__ void __launch_bounds__(LA_THREADS) decay_linear_attention_kernel(cons
   };
   if (has0) store_column(S, to);
   if (has1) store_column(S1, to + dk);
+}
+
+// Logits of decays turned into the decays themselves, in place: sigmoid(z)^inv_root. Rows of
+// `cols` values, `stride` apart.
+__global__ void decay_from_logits_kernel(float* __restrict__ z, long long stride, int cols, long long n,
+                                         float inv_root) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const long long t = i / cols;
+  float* p = z + t * stride + (i - t * cols);
+  *p = root_of_sigmoid(*p, inv_root);
+}
+
+// The product of the alphas of each chunk of every sequence of more than one chunk, per head and
+// key channel: chunk_decay[first chunk of the sequence + c][h * dk + i]. One thread per channel.
+__global__ void chunk_decay_kernel(const float* __restrict__ gate_z, long long gate_stride, float inv_root,
+                                   int is_logit, float* __restrict__ chunk_decay,
+                                   const int* __restrict__ cu_q, int HK, int L) {
+  pdl_trigger();
+  const int seq = blockIdx.z, c = blockIdx.y;
+  const int r0 = cu_q[seq], n = cu_q[seq + 1] - r0;
+  const int num_chunks = (n + L - 1) / L;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  pdl_wait();
+  if (num_chunks <= 1 || c >= num_chunks || e >= HK) return;
+  const int t_end = min(n, (c + 1) * L);
+  float prod = 1.f;
+  for (int t = c * L; t < t_end; ++t) {
+    const float g = gate_z[(size_t)(r0 + t) * gate_stride + e];
+    prod *= is_logit ? root_of_sigmoid(g, inv_root) : g;
+  }
+  chunk_decay[(size_t)(chunk_base(cu_q, seq, L) + c) * HK + e] = prod;
 }
 
 // Launch B: one thread per element of the state and sequence of more than one chunk.
@@ -876,7 +912,8 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
                                           const float* cos, const float* sin, int rot, int silu,
                                           float key_scale, int max_chunks, float* chunks,
                                           cudaStream_t stream, const float* gate_z, long long gate_stride,
-                                          float decay_root, float query_scale, float* chunk_decay) {
+                                          float decay_root, float query_scale, float* chunk_decay,
+                                          int total_rows) {
   if (num_seqs <= 0) return LSE_OK;
   if ((!gate_z && !decay) || (gate_z && (decay_root <= 0.f || gate_stride < (long long)H * dk)) ||
       (gate_z && max_chunks > 1 && !chunk_decay))
@@ -891,40 +928,52 @@ extern "C" int lse_decay_linear_attention(const float* proj, long long stride, f
   a.gate_z = gate_z; a.gate_stride = gate_stride; a.inv_root = gate_z ? 1.f / decay_root : 1.f;
   a.query_scale = query_scale; a.chunk_decay = chunk_decay;
   const bool gated = gate_z != nullptr;
+  // Long portions: many blocks (chunks, slices of a head's columns) read the same logits, so the
+  // decays are made once, in place, by a kernel of their own. Steps of short portions and single
+  // tokens turn the logits into decays as they stage them (one launch fewer).
+  a.gate_is_logit = 1;
+  if (gated && max_chunks > 1 && total_rows > 0) {
+    const long long n = (long long)total_rows * H * dk;
+    launch(decay_from_logits_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, const_cast<float*>(gate_z),
+           gate_stride, H * dk, n, a.inv_root);
+    a.gate_is_logit = 0;
+  }
   a.P = pow2_at_least((dk + LA_RPT - 1) / LA_RPT);
   a.CB = 2 * LA_THREADS / a.P;
-  void (*kernel)(LinAttnArgs) =
-      gated ? (a.P == 1 ? decay_linear_attention_kernel<1, true>
-               : a.P == 2 ? decay_linear_attention_kernel<2, true>
-               : a.P == 4 ? decay_linear_attention_kernel<4, true>
-               : a.P == 8 ? decay_linear_attention_kernel<8, true>
-               : a.P == 16 ? decay_linear_attention_kernel<16, true>
-                           : decay_linear_attention_kernel<32, true>)
-            : (a.P == 1 ? decay_linear_attention_kernel<1, false>
-               : a.P == 2 ? decay_linear_attention_kernel<2, false>
-               : a.P == 4 ? decay_linear_attention_kernel<4, false>
-               : a.P == 8 ? decay_linear_attention_kernel<8, false>
-               : a.P == 16 ? decay_linear_attention_kernel<16, false>
-                           : decay_linear_attention_kernel<32, false>);
+#define LSE_LA_KERNEL(MODE)                                          \
+  (a.P == 1 ? decay_linear_attention_kernel<1, MODE>                 \
+   : a.P == 2 ? decay_linear_attention_kernel<2, MODE>               \
+   : a.P == 4 ? decay_linear_attention_kernel<4, MODE>               \
+   : a.P == 8 ? decay_linear_attention_kernel<8, MODE>               \
+   : a.P == 16 ? decay_linear_attention_kernel<16, MODE>             \
+               : decay_linear_attention_kernel<32, MODE>)
+  void (*kernel)(LinAttnArgs) = gated ? LSE_LA_KERNEL(1) : LSE_LA_KERNEL(0);
+  void (*kernel_add)(LinAttnArgs) = gated ? LSE_LA_KERNEL(2) : kernel;
+#undef LSE_LA_KERNEL
   a.L = lse_linear_attention_chunk();
   a.phase = 0;
   const int slices = (dv + a.CB - 1) / a.CB;
+  const int tile = gated ? LA_TT_GATED : LA_TT;
   const size_t smem =
-      2 * ((size_t)(gated ? 3 : 2) * LA_TT * a.P * (LA_RPT + LA_PAD) + (size_t)LA_TT * a.CB) * sizeof(float);
+      2 * ((size_t)(gated ? 3 : 2) * tile * a.P * (LA_RPT + LA_PAD) + (size_t)tile * a.CB) * sizeof(float);
   static bool configured[2][33] = {};
   if (!configured[gated][a.P]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (gated ? 160 : 112) * 1024) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        (kernel_add != kernel &&
+         cudaFuncSetAttribute(kernel_add, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess))
       return LSE_LAUNCH_FAILED;
     configured[gated][a.P] = true;
   }
   launch(kernel, dim3(H * slices, max_chunks, num_seqs), LA_THREADS, smem, stream, a);
   if (max_chunks > 1) {
     const size_t per_state = (size_t)H * dv * dk;
+    if (gated)
+      launch(chunk_decay_kernel, dim3((unsigned)((H * dk + 127) / 128), max_chunks, num_seqs), 128, 0, stream, gate_z,
+             gate_stride, a.inv_root, a.gate_is_logit, chunk_decay, cu_q, H * dk, a.L);
     launch(chain_chunk_states_kernel, dim3((unsigned)((per_state + 255) / 256), num_seqs), 256, 0, stream,
            chunks, state, decay, cu_q, slots, H, dv, dk, a.L, (const float*)(gated ? chunk_decay : nullptr));
     a.phase = 2;
-    launch(kernel, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
+    launch(kernel_add, dim3(H * slices, max_chunks - 1, num_seqs), LA_THREADS, smem, stream, a);
   }
   return LSE_CHECK_LAUNCH();
 }

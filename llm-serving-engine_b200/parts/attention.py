@@ -53,6 +53,16 @@ import torch
 from .base import MIXERS, POSITION_ENCODINGS, Mixer, PagedKVNeed, ParamDecl, project_into
 
 
+def rows_to_whole_vectors(w, multiple: int = 8):
+    """A fused projection matrix with zero rows behind its last, so that a row of the product is
+    a whole number of 16-byte vectors whatever the number of gate rows is (the kernels that read
+    the product then work on vectors; what lies behind the last head is never read)."""
+    extra = (-w.shape[0]) % multiple
+    if not extra:
+        return w
+    return torch.cat([w, w.new_zeros(extra, w.shape[1])], 0).contiguous()
+
+
 @dataclass(frozen=True)
 class AttentionSpec:
     hidden_size: int
@@ -165,6 +175,7 @@ class PagedAttention(Mixer):
             self.q_norm_weight = torch.ones(self.q_size if row else s.head_dim, dtype=torch.float32, device=self.env.device)
             self.k_norm_weight = torch.ones(self.kv_size if row else s.head_dim, dtype=torch.float32, device=self.env.device)
         if self.by_rows:  # the kernel fills the heads up; only the output projection meets the padded heads
+            self.qkv_weight = rows_to_whole_vectors(self.qkv_weight)
             if self.kernel_dim != self.value_dim:
                 o = self.o_weight.new_zeros(s.hidden_size, s.num_heads, self.kernel_dim)
                 o[:, :, :self.value_dim] = self.o_weight.view(s.hidden_size, s.num_heads, self.value_dim)

@@ -24,6 +24,7 @@ from dataclasses import dataclass
 
 import torch
 
+from .attention import rows_to_whole_vectors
 from .base import MIXERS, Mixer, PagedKVNeed, ParamDecl, project_into
 
 
@@ -76,7 +77,7 @@ class DifferentialAttention(Mixer):
         # query rows from (group, head in group, map) to (group, map, head in group)
         q = w[: self.q_size].view(s.num_kv_heads, self.group, 2, s.head_dim, s.hidden_size)
         q = q.permute(0, 2, 1, 3, 4).reshape(self.q_size, s.hidden_size)
-        self.qkv_weight = torch.cat([q, w[self.q_size:]], 0).contiguous()
+        self.qkv_weight = rows_to_whole_vectors(torch.cat([q, w[self.q_size:]], 0))
         self.o_weight = params["o.weight"]
         one = (params["lam.q1"].float() * params["lam.k1"].float()).sum().exp()
         two = (params["lam.q2"].float() * params["lam.k2"].float()).sum().exp()
