@@ -102,7 +102,7 @@ streams_read_norm_kernel(const float* __restrict__ x, const float* __restrict__ 
 // a few-rows product (taken: zeros are left behind).
 // MS: the most streams this instantiation holds in registers (S <= MS).
 template <typename TY, typename TO, int V, int MS>
-__global__ void __launch_bounds__(SM_THREADS, MS <= 4 ? 4 : 0)  // four blocks an SM while the streams fit 64 registers
+__global__ void __launch_bounds__(SM_THREADS)
 streams_write_kernel(float* __restrict__ x, const TY* y, const float* __restrict__ scale,
                      const float* __restrict__ mix, const float* __restrict__ outw, int W, int S,
                      const float* __restrict__ then_read, const float* __restrict__ then_w, float then_eps,
