@@ -182,7 +182,7 @@ int lse_decay_linear_attention(const float* proj, long long stride, float* out, 
 // out[t, s*W + i] = x[t, i] * scale for every stream s.
 int lse_streams_spread(const float* x, float* out, int T, int W, int S, float scale, cudaStream_t stream);
 
-// out[r] = u / rms(u) * w with u = sum_s read[s] * x[t, s], t = rows ? rows[r] : r. S <= 8.
+// out[r] = u / rms(u) * w with u = sum_s read[s] * x[t, s], t = rows ? rows[r] : r. S <= 16.
 int lse_streams_read_norm(const float* x, const float* read, const float* w, float eps, void* out,
                           int out_dtype, const int* rows, int n_rows, int W, int S, cudaStream_t stream);
 
