@@ -196,11 +196,18 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
     m = m_new;
   }
   if (row_valid) {
-    T* o = (T*)a.out + (size_t)(si.q_start + qi) * a.out_row_stride + (size_t)head * D;
+    const size_t at = (size_t)(si.q_start + qi) * a.out_row_stride + (size_t)head * D;
     if (a.sinks && l > 0.f) l += Exp<T>::f(a.sinks[head] - m);
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (a.out_f32) {
+      float* o = (float*)a.out + at;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) o[sub + 4 * i] = Num<T>::from_float(acc[i] * inv);
+      for (int i = 0; i < DPT; ++i) o[sub + 4 * i] = acc[i] * inv;
+    } else {
+      T* o = (T*)a.out + at;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) o[sub + 4 * i] = Num<T>::from_float(acc[i] * inv);
+    }
   }
 }
 
@@ -423,9 +430,16 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
     // with a sink the scores are finished ones (options), so m_r is in their natural units
     if (a.sinks && l_r[rr] > 0.f) l_r[rr] += expf(a.sinks[head] - m_r[rr]);
     const float inv = l_r[rr] > 0.f ? 1.f / l_r[rr] : 0.f;
-    bf16* dst = (bf16*)a.out +
-                (size_t)(si.q_start + q0 + warp * 16 + g + rr * 8) * a.out_row_stride +
-                (size_t)head * D + t4 * 2;
+    const size_t at = (size_t)(si.q_start + q0 + warp * 16 + g + rr * 8) * a.out_row_stride +
+                      (size_t)head * D + t4 * 2;
+    if (a.out_f32) {
+      float* dst = (float*)a.out + at;
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+        *reinterpret_cast<float2*>(dst + db * 8) = make_float2(o[db][rr * 2] * inv, o[db][rr * 2 + 1] * inv);
+      continue;
+    }
+    bf16* dst = (bf16*)a.out + at;
 #pragma unroll
     for (int db = 0; db < DB; ++db)
       *reinterpret_cast<uint32_t*>(dst + db * 8) =
@@ -458,7 +472,8 @@ constexpr int MERGE_SPLITS = 64;  // most context partitions per (sequence, head
 template <typename T, int GT>
 __device__ __noinline__ void merge_partitions(const float* __restrict__ parts, int num_splits,
                                               int heads_here, T* __restrict__ out,
-                                              const float* __restrict__ sinks = nullptr) {
+                                              const float* __restrict__ sinks = nullptr,
+                                              float* __restrict__ out32 = nullptr) {
   // parts: partition 0 of this block's first head; heads are num_splits * (D + 2) floats apart.
   // out: this token's row at the first head.
   __shared__ float sm_w[GT][MERGE_SPLITS], sm_L[GT];
@@ -501,7 +516,8 @@ __device__ __noinline__ void merge_partitions(const float* __restrict__ parts, i
       for (int u = 0; u < 8; ++u) A += v[u] * sm_w[gq][min(s0 + u, MERGE_SPLITS - 1)];
     }
     const float L = sm_L[gq];
-    out[idx] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+    if (out32) out32[idx] = L > 0.f ? A / L : 0.f;  // unrounded, where the caller asked for float32
+    else out[idx] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
   }
 }
 
@@ -685,9 +701,10 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
     }
     const int h = h0 + gq;
     if (a.num_splits == 1) {
-      T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      const size_t at = (size_t)tok * a.out_row_stride + (size_t)h * D + d;
       if (a.sinks && L > 0.f) L += Exp<T>::f(a.sinks[h] - M);
-      o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+      if (a.out_f32) ((float*)a.out)[at] = L > 0.f ? A / L : 0.f;
+      else ((T*)a.out)[at] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
     } else {
       float* part = a.scratch + LSE_ATTN_COUNTERS +
                     (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
@@ -716,7 +733,8 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   merge_partitions<T, GT>(
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, heads_here, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D,
-      a.sinks ? a.sinks + h0 : nullptr);
+      a.sinks ? a.sinks + h0 : nullptr,
+      a.out_f32 ? (float*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D : nullptr);
 }
 
 #if LSE_HEAD_DIM == 64
@@ -1310,8 +1328,9 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
     const int h = h0 + gq;
     if (a.num_splits == 1) {
       if (a.sinks && L > 0.f) L += Exp<T>::f(a.sinks[h] - M);  // a sink joins the denominator once
-      T* op = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
-      op[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+      const size_t at = (size_t)tok * a.out_row_stride + (size_t)h * D + d;
+      if (a.out_f32) ((float*)a.out)[at] = L > 0.f ? A / L : 0.f;
+      else ((T*)a.out)[at] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
     } else {
       float* part = a.scratch + LSE_ATTN_COUNTERS +
                     (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
@@ -1354,7 +1373,8 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   merge_partitions<T, HEADS>(
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D,
-      a.sinks ? a.sinks + h0 : nullptr);  // after the merge, once
+      a.sinks ? a.sinks + h0 : nullptr,  // after the merge, once
+      a.out_f32 ? (float*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D : nullptr);
 }
 
 // The same computation fed by TMA: every warp has PER slots of 128-byte-swizzled shared memory, each
@@ -1642,7 +1662,7 @@ static bool args_ok(const LseAttnArgs* a) {
          a->num_kv_heads > 0 && a->num_heads % a->num_kv_heads == 0 && a->page_tokens > 0 &&
          a->window >= 0 && a->chunk >= 0 && a->keep_first >= 0 && !(a->keep_first > 0 && a->chunk > 0) &&
          (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
-         a->ctx_lens && a->cu_q;
+         a->ctx_lens && a->cu_q && (a->out_f32 == 0 || (a->out_f32 == 1 && !a->qkv_sums));
 }
 
 template <typename T>
@@ -1650,7 +1670,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
   // served by the CUDA-core kernel only (sinks: also by the tensor-core kernel for groups of up to 8)
-  const bool options = a->head_scale || a->slopes || a->chunk > 0 || (a->sinks && G > 8) ||
+  const bool options = a->head_scale || a->slopes || a->chunk > 0 || ((a->sinks || a->out_f32) && G > 8) ||
                        (a->keep_first > 0 && a->window > 0);
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
   // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
@@ -1680,7 +1700,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     // partitions: 30.6 against 27.3) the other one is taken.
     const bool ring_can = G <= 8 && ps >= 4 && pool_rows > 0 && pool_rows < (1LL << 31);
     if (a->qkv_sums && G > 8) return LSE_BAD_ARGUMENT;  // only the kernel for groups of up to 8 makes its own queries
-    if (ring_can && !a->qkv_sums && !a->sinks && (a->force_simt == 3 ||
+    if (ring_can && !a->qkv_sums && !a->sinks && !a->out_f32 && (a->force_simt == 3 ||
                      (a->force_simt == 0 && a->num_splits == 1 && blocks >= 10LL * sms))) {
       constexpr int PER = 1;
       constexpr int smem = PER * DEC_WARPS * 2 * ring::TILE_BYTES + 1024;
@@ -1789,7 +1809,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
 #if LSE_HEAD_DIM == 64
   } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a) &&
-             !(a->head_scale || a->slopes || a->chunk > 0 || a->sinks || a->keep_first > 0)) {
+             !(a->head_scale || a->slopes || a->chunk > 0 || a->sinks || a->keep_first > 0 || a->out_f32)) {
     // 128-row tiles, like the mma.sync kernel
     return atc::launch_prefill(a, a->num_rows, a->num_pages * a->num_kv_heads * a->page_tokens,
                                a->error_flag, stream);

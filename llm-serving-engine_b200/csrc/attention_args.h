@@ -66,6 +66,11 @@ struct LseAttnArgs {
   //   reads the sequence's first keep_first keys, as far as they lie before it. The pages of those
   //   keys must still be held.
   int keep_first;
+  // 1 (with dtype LSE_BF16): `out` is float32 [rows, out_row_stride]; the results leave the
+  // kernels unrounded, for a caller that still subtracts or norms them. Served by the CUDA-core
+  // kernels, the mma.sync kernel for portions and the tensor-core single-token kernel for groups
+  // of up to 8 heads.
+  int out_f32;
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)

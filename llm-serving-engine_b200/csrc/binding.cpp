@@ -324,9 +324,11 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   check_i32(cu_q, "cu_q");
   TORCH_CHECK(out.dim() == 2 && out.size(0) == q.size(0) && out.size(1) == num_heads * D,
               "paged_attention: out must be [T, heads*head_dim]");
-  TORCH_CHECK(out.scalar_type() == q.scalar_type() && k_pages.scalar_type() == q.scalar_type() &&
+  // a bfloat16 call may ask for its results unrounded, in a float32 out
+  const bool out_f32 = q.scalar_type() == torch::kBFloat16 && out.scalar_type() == torch::kFloat32;
+  TORCH_CHECK((out.scalar_type() == q.scalar_type() || out_f32) && k_pages.scalar_type() == q.scalar_type() &&
                   v_pages.scalar_type() == q.scalar_type(),
-              "paged_attention: q, out and pages must share a dtype");
+              "paged_attention: q, out and pages must share a dtype (out may be float32 beside bfloat16)");
   TORCH_CHECK(k_pages.dim() == 4 && k_pages.size(1) == num_kv_heads && k_pages.size(3) == D &&
                   v_pages.sizes() == k_pages.sizes(),
               "paged_attention: pages must be [pages, kv_heads, page_tokens, head_dim]");
@@ -340,6 +342,7 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   a.dtype = dtype_code(q, "q");
   a.q = q.data_ptr();
   a.q_row_stride = q.stride(0);
+  a.out_f32 = out_f32 ? 1 : 0;
   a.out = out.data_ptr();
   a.out_row_stride = out.stride(0);
   a.k_pages = k_pages.data_ptr();
@@ -1223,8 +1226,9 @@ void differential_combine(const Tensor& a, const Tensor& gate, int64_t gate_col0
   check_cuda(out, "out");
   TORCH_CHECK(a.dim() == 2 && a.size(1) == 2 * H * Dp && gate.dim() == 2 && gate.size(0) == a.size(0) &&
                   gate_col0 >= 0 && gate_col0 + H <= gate.size(1) && out.dim() == 2 && out.size(0) == a.size(0) &&
-                  out.size(1) == H * Dv && out.scalar_type() == a.scalar_type(),
-              "differential_combine: need a [T, 2*heads*head_dim], gate columns inside gate, out [T, heads*value_dim] of a's dtype");
+                  out.size(1) == H * Dv &&
+                  (out.scalar_type() == a.scalar_type() || a.scalar_type() == torch::kFloat32),
+              "differential_combine: need a [T, 2*heads*head_dim], gate columns inside gate, out [T, heads*value_dim] of a's dtype (or a in float32)");
   done(lse_differential_combine(a.data_ptr(), out_code(a, "a"), gate.data_ptr<float>() + gate_col0, gate.size(1),
                                 (int)a.size(0), (int)H, (int)n, (int)Dp, (int)Dv, (float)lam, (float)eps,
                                 (float)out_scale, out.data_ptr(), out_code(out, "out"), stream()),

@@ -209,7 +209,8 @@ int lse_qkv_norm_rope_write(const float* proj, long long stride, int T, int nq, 
 
 // a [T, 2H*Dp]: for every key group of n heads, the heads' first attention maps, then their second
 // ones. out[t, h] (Dv values) = o / rms(o) * out_scale * sigmoid(gate[t*gate_stride + h]),
-// o = a1 - lam * a2 over the first Dv dims. a and out have the same dtype. Dv <= 256.
+// o = a1 - lam * a2 over the first Dv dims. a and out have the same dtype, or a is float32 and out
+// bfloat16. Dv <= 256.
 int lse_differential_combine(const void* a, int a_dtype, const float* gate, long long gate_stride, int T,
                              int H, int n, int Dp, int Dv, float lam, float eps, float out_scale, void* out,
                              int out_dtype, cudaStream_t stream);

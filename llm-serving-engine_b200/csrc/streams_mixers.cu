@@ -511,14 +511,15 @@ extern "C" int lse_differential_combine(const void* a, int a_dtype, const float*
                                         int T, int H, int n, int Dp, int Dv, float lam, float eps,
                                         float out_scale, void* out, int out_dtype, cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  if (H <= 0 || n <= 0 || H % n || Dv <= 0 || Dv > 256 || Dp < Dv || a_dtype != out_dtype) return LSE_BAD_ARGUMENT;
+  if (H <= 0 || n <= 0 || H % n || Dv <= 0 || Dv > 256 || Dp < Dv) return LSE_BAD_ARGUMENT;
   const unsigned blocks = (unsigned)(((long long)T * H + DC_WARPS - 1) / DC_WARPS);
-  if (a_dtype == LSE_BF16)
-    launch(differential_combine_kernel<bf16, bf16>, blocks, DC_WARPS * 32, 0, stream, (const bf16*)a, gate,
-           gate_stride, H, n, Dp, Dv, lam, eps, out_scale, (bf16*)out, T);
-  else if (a_dtype == LSE_F32)
-    launch(differential_combine_kernel<float, float>, blocks, DC_WARPS * 32, 0, stream, (const float*)a, gate,
-           gate_stride, H, n, Dp, Dv, lam, eps, out_scale, (float*)out, T);
+#define LSE_DC(TA, TO)                                                                                        \
+  launch(differential_combine_kernel<TA, TO>, blocks, DC_WARPS * 32, 0, stream, (const TA*)a, gate, gate_stride, \
+         H, n, Dp, Dv, lam, eps, out_scale, (TO*)out, T)
+  if (a_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_DC(bf16, bf16);
+  else if (a_dtype == LSE_F32 && out_dtype == LSE_F32) LSE_DC(float, float);
+  else if (a_dtype == LSE_F32 && out_dtype == LSE_BF16) LSE_DC(float, bf16);
   else return LSE_BAD_ARGUMENT;
+#undef LSE_DC
   return LSE_CHECK_LAUNCH();
 }

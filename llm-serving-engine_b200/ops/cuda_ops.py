@@ -412,12 +412,13 @@ class CudaOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan, head_scale=None, slopes=None,
-                        chunk=0, sinks=None, keep_first=0):
+                        chunk=0, sinks=None, keep_first=0, out_dtype=None):
         """``head_scale`` / ``slopes`` (float32 ``[heads]``) and ``chunk``: a factor per head on the
         score, ``slope_h * (i - j)`` taken off it, and keys limited to the query's chunk. ``sinks``
         (float32 ``[heads]``): ``exp(sink_h)`` joins the softmax's denominator. ``keep_first``: with
-        a window, the sequence's first ``keep_first`` keys stay visible beside the window's."""
-        out = torch.empty(q.shape[0], num_heads * head_dim, dtype=q.dtype, device=q.device)
+        a window, the sequence's first ``keep_first`` keys stay visible beside the window's.
+        ``out_dtype=torch.float32`` beside bfloat16 queries: the results are handed on unrounded."""
+        out = torch.empty(q.shape[0], num_heads * head_dim, dtype=out_dtype or q.dtype, device=q.device)
         n_tiles = int(plan["tiles"].shape[0])
         n_dec = int(plan["decode_seqs"].shape[0])
         splits = step.decode_splits if step.decode_splits else self.decode_splits(
@@ -777,11 +778,11 @@ class CudaOps:
         """``a [T, 2 * heads * head_dim]`` (per key group: its heads' first maps, then their second
         ones) to ``[T, heads * value_dim]``: ``o = a1 - lam * a2``, divided by its root mean square,
         times ``out_scale`` and ``sigmoid(proj[t, gate_col0 + head])``."""
-        out = torch.empty(a.shape[0], num_heads * value_dim, dtype=a.dtype, device=a.device)
+        out = torch.empty(a.shape[0], num_heads * value_dim, dtype=out_dtype, device=a.device)
         self.ext.differential_combine(a, proj, int(gate_col0), int(num_heads), int(group), int(head_dim),
                                       int(value_dim), float(lam), float(eps), float(out_scale), out)
         self.launches += 1
-        return out if out.dtype == out_dtype else out.to(out_dtype)
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):

@@ -15,7 +15,9 @@ The paged attention kernels run it as ``2H`` query heads on ``2G`` key heads: th
 reordered when they are bound, so that the query heads of one (group, map) follow each other and
 the kernels' rule "query head j reads key head j // (H/G)" pairs every map with its own keys; every
 value head is written into the pages of both of its maps' key heads. Heads are filled up to the
-kernels' head size by the kernel that writes them.
+kernels' head size by the kernel that writes them. The kernels hand the two maps' results on in
+float32 in the bfloat16 path too: the difference of two nearly equal maps would otherwise carry
+their rounding.
 """
 
 from __future__ import annotations
@@ -118,7 +120,8 @@ class DifferentialAttention(Mixer):
         a = ops.paged_attention(
             q, num_heads=2 * s.num_heads, num_kv_heads=2 * s.num_kv_heads, head_dim=self.kernel_dim,
             scale=s.scale, window=s.window, k_pages=cache.k, v_pages=cache.v, block_tables=tables,
-            page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()])
+            page_tokens=cache.page_tokens, step=step, plan=step.plans[self.plan_key()],
+            out_dtype=torch.float32)  # the maps are subtracted before anything is rounded
         o = ops.differential_combine(
             a, qkv, gate_col0=self.q_size + self.k_size + self.v_size, num_heads=s.num_heads, group=self.group,
             head_dim=self.kernel_dim, value_dim=s.value_dim, lam=self.lam, eps=s.eps, out_scale=s.out_scale,

@@ -137,7 +137,7 @@ class PlainOps:
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan=None, head_scale=None,
-                        slopes=None, chunk=0, sinks=None, keep_first=0):
+                        slopes=None, chunk=0, sinks=None, keep_first=0, out_dtype=None):
         T, D = q.shape[0], head_dim
         qkv = q
         q = q[:, : num_heads * D].float().reshape(T, num_heads, D)
@@ -168,7 +168,7 @@ class PlainOps:
                 sc = torch.cat([sc, sinks.float()[:, None, None].expand(-1, n, 1)], -1)
                 v = torch.cat([v, torch.zeros_like(v[:1])], 0)
             out[a:b] = torch.einsum("hts,shd->thd", sc.softmax(-1), v)
-        return out.view(T, num_heads * D).to(qkv.dtype)
+        return out.view(T, num_heads * D).to(out_dtype or qkv.dtype)
 
     def norm_rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, values_are_keys, q_weight,
                            k_weight, eps, positions, token_seq, cos, sin, k_pages, v_pages,

@@ -195,7 +195,7 @@ def test_stretched_frequencies_against_the_formula_written_out():
 
 
 # ----------------------------------------------------------------------------- attention with sinks and a window, through the mixer's ops
-def attend_paged(ops, dtype, H, G, D, page_tokens, window, n_rows, ctx, splits, sinks, q, k, v, scale):
+def attend_paged(ops, dtype, H, G, D, page_tokens, window, n_rows, ctx, splits, sinks, q, k, v, scale, out_dtype=None):
     """One sequence of ``ctx`` tokens whose last ``n_rows`` are this step's queries."""
     b = batch([n_rows], [ctx - n_rows], [0])
     b.decode_splits = splits if n_rows == 1 else 0
@@ -209,7 +209,7 @@ def attend_paged(ops, dtype, H, G, D, page_tokens, window, n_rows, ctx, splits, 
     return ops.paged_attention(
         q[ctx - n_rows:].reshape(n_rows, H * D).to(dtype).cuda().contiguous(), num_heads=H, num_kv_heads=G,
         head_dim=D, scale=scale, window=window, k_pages=kp, v_pages=vp, block_tables=tables, page_tokens=page_tokens,
-        step=b, plan=plan, sinks=None if sinks is None else sinks.float().cuda())
+        step=b, plan=plan, sinks=None if sinks is None else sinks.float().cuda(), out_dtype=out_dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -255,11 +255,31 @@ def test_a_far_key_among_hundreds_without_a_window(ops, dtype, n_rows, splits):
     assert (ref[-1] - v[5].to(F)).abs().max().item() < 0.05
 
 
+@pytest.mark.parametrize("n_rows,splits", [(1, 1), (1, 3), (50, 0), (2, 0)])
+@pytest.mark.parametrize("H,G,D", [(4, 2, 64), (4, 4, 128), (12, 1, 64), (3, 3, 48), (2, 1, 160)])
+def test_bfloat16_attention_hands_its_results_on_in_float32(ops, n_rows, splits, H, G, D):
+    """Asked for a float32 out, every kernel that serves the call gives what it gives in
+    bfloat16 before the last rounding: the two agree to that rounding, and the float32 one is the
+    nearer to the plain result."""
+    ctx = 200
+    q, k, v = rnd(ctx, H, D, seed=1, scale=0.3), rnd(ctx, G, D, seed=2, scale=0.3), rnd(ctx, G, D, seed=3)
+    args = (ops, torch.bfloat16, H, G, D, 16, 0, n_rows, ctx, splits, None, q, k, v, 0.3)
+    wide = attend_paged(*args, out_dtype=torch.float32)
+    narrow = attend_paged(*args)
+    assert wide.dtype == torch.float32 and narrow.dtype == torch.bfloat16
+    r = lambda t: t.bfloat16().to(F)  # the operands the bfloat16 kernels see
+    ref = pl.attend(r(q), r(k), r(v), 0.3, pl.causal(ctx), None)[ctx - n_rows:].reshape(n_rows, H * D)
+    close(narrow, wide.cpu(), 8e-3)
+    assert (wide.double().cpu() - ref).abs().max() <= (narrow.double().cpu() - ref).abs().max() + 1e-6
+    close(wide, ref, 6e-3)
+
+
 # ----------------------------------------------------------------------------- the two maps combined
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,a_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                           (torch.bfloat16, torch.float32)])  # maps in float32, result rounded once
 @pytest.mark.parametrize("T,H,n,Dp,Dv", [(5, 4, 2, 32, 32), (3, 3, 3, 48, 24), (7, 2, 1, 64, 50), (2, 6, 2, 16, 10)])
-def test_differential_combine(ops, dtype, T, H, n, Dp, Dv):
-    a = rnd(T, 2 * H * Dp, seed=1).to(dtype)
+def test_differential_combine(ops, dtype, a_dtype, T, H, n, Dp, Dv):
+    a = rnd(T, 2 * H * Dp, seed=1).to(a_dtype)
     gate = rnd(T, 11 + H, seed=2)
     lam, eps, out_scale = 0.37, 1e-5, 0.6
     got = ops.differential_combine(a.cuda(), gate.cuda(), gate_col0=11, num_heads=H, group=n, head_dim=Dp,
@@ -532,3 +552,34 @@ def test_greedy_bfloat16_picks_tokens_the_plain_model_also_ranks_first(lanilorn_
         logits = pl.model_logits(lanilorn_dirs["L1"], p + gen)[len(p) - 1 : -1]
         for t, row in zip(gen, logits):
             assert float(row.max() - row[t]) <= 0.03 * float(row.abs().max())
+
+
+def wanted_subsets(make_runner, folder, vocab):
+    """Steps that want some rows, one row or none: the model's last norm then reads only those rows,
+    and a step's last write into the streams is carried out without a read behind it."""
+    from llmserve_b200.engine.batch import StepEntry
+
+    reqs = traces.make_requests([41, 30], vocab, seed=13)
+    exp = {r: pl.model_logits(folder, t) for r, t in reqs.items()}
+    runner = make_runner()
+    a, b = reqs["r0"], reqs["r1"]
+    steps = [([("r0", a[:17], [3, 16]), ("r1", b[:9], [])], None),
+             ([("r0", a[17:18], []), ("r1", b[9:22], [0, 12])], None),
+             ([("r0", a[18:19], [0]), ("r1", b[22:23], [])], None),
+             ([("r0", a[19:41], [21]), ("r1", b[23:30], [6, 2])], None)]
+    at = {"r0": 0, "r1": 0}
+    for entries, _ in steps:
+        logits = runner.run([StepEntry(r, t, w) for r, t, w in entries]).float().cpu()
+        row = 0
+        for r, t, w in entries:
+            for k in w:
+                ref = exp[r][at[r] + k]
+                assert (logits[row] - ref).abs().max().item() <= 2e-4 + 5e-5 * ref.abs().max().item(), (r, at[r] + k)
+                row += 1
+            at[r] += len(t)
+        assert row == logits.shape[0]
+
+
+@pytest.mark.parametrize("name", ["L1", "L2"])
+def test_steps_that_want_some_rows_or_none(lanilorn_dirs, name):
+    wanted_subsets(lambda: gpu_runner(lanilorn_dirs[name], name, 16, "float32"), lanilorn_dirs[name], LANILORN_TINY[name]["config"]["vocab"])

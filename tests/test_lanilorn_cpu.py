@@ -160,3 +160,34 @@ def test_greedy_generation_through_the_scheduler(lanilorn_dirs):
     outs = m.generate(prompts, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
     for o, p in zip(outs, prompts):
         assert o.outputs[0].token_ids == pl.greedy(lanilorn_dirs["L1"], p, 8), p
+
+
+def wanted_subsets(make_runner, folder, vocab):
+    """Steps that want some rows, one row or none: the model's last norm then reads only those rows,
+    and a step's last write into the streams is carried out without a read behind it."""
+    from llmserve_b200.engine.batch import StepEntry
+
+    reqs = traces.make_requests([41, 30], vocab, seed=13)
+    exp = {r: pl.model_logits(folder, t) for r, t in reqs.items()}
+    runner = make_runner()
+    a, b = reqs["r0"], reqs["r1"]
+    steps = [([("r0", a[:17], [3, 16]), ("r1", b[:9], [])], None),
+             ([("r0", a[17:18], []), ("r1", b[9:22], [0, 12])], None),
+             ([("r0", a[18:19], [0]), ("r1", b[22:23], [])], None),
+             ([("r0", a[19:41], [21]), ("r1", b[23:30], [6, 2])], None)]
+    at = {"r0": 0, "r1": 0}
+    for entries, _ in steps:
+        logits = runner.run([StepEntry(r, t, w) for r, t, w in entries]).float().cpu()
+        row = 0
+        for r, t, w in entries:
+            for k in w:
+                ref = exp[r][at[r] + k]
+                assert (logits[row] - ref).abs().max().item() <= 2e-4 + 5e-5 * ref.abs().max().item(), (r, at[r] + k)
+                row += 1
+            at[r] += len(t)
+        assert row == logits.shape[0]
+
+
+@pytest.mark.parametrize("name", ["L1", "L2"])
+def test_steps_that_want_some_rows_or_none(lanilorn_dirs, name):
+    wanted_subsets(lambda: cpu_runner(lanilorn_dirs[name], name, 16), lanilorn_dirs[name], LANILORN_TINY[name]["config"]["vocab"])

@@ -35,7 +35,7 @@ class AttnArgs(ctypes.Structure):
         ("num_rows", ctypes.c_longlong), ("num_pages", ctypes.c_longlong), ("error_flag", ctypes.c_void_p),
         ("qkv_sums", ctypes.c_void_p), ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p),
         ("head_scale", ctypes.c_void_p), ("slopes", ctypes.c_void_p), ("chunk", ctypes.c_int),
-        ("sinks", ctypes.c_void_p), ("keep_first", ctypes.c_int),
+        ("sinks", ctypes.c_void_p), ("keep_first", ctypes.c_int), ("out_f32", ctypes.c_int),
     ]
 
 
