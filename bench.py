@@ -645,19 +645,19 @@ def lanilorn_layers(width, heads, kv_heads, head_dim, ff, window=1024, state_dim
     layer's size."""
     mlp = {"kind": "dense", "ff": ff}
     lin = max(1, width // state_dim)
-    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": lin, "dim": state_dim, "vdim": state_dim, "tau": 16.0,
+    gla = {"type": "gla", "mlp": mlp, "mixer": {"heads": lin, "dim": state_dim, "vdim": state_dim, "tau": 8.0,
                                                  "decay_rank": rank}}
     att = {"type": "attention", "mlp": mlp, "mixer": {
         "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
         "mask": {"size": window},
-        "rot": {"base": 250000.0, "dims": head_dim // 2,
-                "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}}}}
+        "rot": {"base": 500000.0, "dims": head_dim // 2,
+                "scaling": {"factor": 4.0, "fast": 16.0, "original": 4096, "slow": 2.0}}}}
     half, kv_half = max(1, heads // 2), max(1, kv_heads // 2)
     while half % kv_half:
         kv_half -= 1
     diff = {"type": "attention_2", "mlp": mlp, "mixer": {
         "heads": half, "kv_heads": kv_half, "dim": head_dim, "vdim": 2 * head_dim, "scale": head_dim ** -0.5,
-        "diff": 0.5, "q_temp": {"coef": 0.1, "every": 256}}}
+        "diff": 0.4, "q_temp": {"coef": 0.1, "every": 256}}}
     return [gla, att, diff, att]
 
 
