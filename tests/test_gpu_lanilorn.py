@@ -174,26 +174,6 @@ def test_rows_are_normed_turned_filled_up_and_find_their_pages(ops, dtype, nq, n
     assert torch.equal(got2, got)
 
 
-def test_stretched_frequencies_against_the_formula_written_out():
-    """The tables of the position part: pairs that turn fast keep their frequency, slow ones are
-    stretched by the factor, the ones between are blended, and both tables carry the factor's magnitude."""
-    from llmserve_b200.parts.base import BuildEnv
-    from llmserve_b200.parts.positions import RotaryPositionEncoding, RotarySpec
-
-    env = BuildEnv(ops=None, dtype=torch.float32, device=torch.device("cpu"), max_positions=50)
-    for dims, base, sc in [(12, 10000.0, dict(factor=4.0, original=64, fast=16.0, slow=2.0)),
-                           (32, 250.0, dict(factor=16.0, original=40, fast=4.0, slow=0.5)),
-                           (6, 50.0, dict(factor=2.0, original=8, fast=1.0, slow=1.0))]:
-        spec = RotarySpec(head_dim=dims, theta=base, scaling_type="yarn", factor=sc["factor"],
-                          original_max_positions=sc["original"], yarn_fast=sc["fast"], yarn_slow=sc["slow"])
-        cos, sin = RotaryPositionEncoding(spec, env).rotary_tables()
-        f, mag = pl.yarn_frequencies(dims, base, sc)
-        ang = torch.arange(50, dtype=F)[:, None] * f[None, :]
-        assert torch.allclose(cos.double(), ang.cos() * mag, atol=1e-6) and torch.allclose(sin.double(), ang.sin() * mag, atol=1e-6)
-        plain = base ** (-2.0 * torch.arange(dims // 2, dtype=F) / dims)
-        assert (f <= plain + 1e-15).all() and (f >= plain / sc["factor"] - 1e-15).all() and mag > 1.0
-
-
 # ----------------------------------------------------------------------------- attention with sinks and a window, through the mixer's ops
 def attend_paged(ops, dtype, H, G, D, page_tokens, window, n_rows, ctx, splits, sinks, q, k, v, scale, out_dtype=None):
     """One sequence of ``ctx`` tokens whose last ``n_rows`` are this step's queries."""
